@@ -6,12 +6,12 @@ import ctypes as C
 
 from ..csrc.build import host_library
 
-ABI_VERSION = 4
+ABI_VERSION = 5
 I32P = C.POINTER(C.c_int32)
 
 
 class GroupSpecC(C.Structure):
-    _fields_ = [("page_size", C.c_int32), ("window", C.c_int32), ("num_pages", C.c_int32)]
+    _fields_ = [("page_size", C.c_int32), ("window", C.c_int32), ("num_pages", C.c_int32), ("keep_first", C.c_int32)]
 
 
 class SchedulerConfigC(C.Structure):

@@ -2,7 +2,8 @@
 
 Per cache group one tensor [num_pages + 1, page_elems]: page 0 is the null page (real memory,
 never handed out). A page holds, for each member layer of the group, K then V for `page_size`
-tokens, each laid out [kv_head][offset][head_dim], so a (page, head) tile is contiguous. One
+tokens, each laid out [kv_head][offset][head_dim] (values with a head size of their own where a
+layer has one), so a (page, head) tile is contiguous. One
 block table per request and group therefore serves all the group's layers (the reference packs
 all layers of a group into one page row too: kelpie-models/kelpie_models/sdk/kv.py:1-34,
 118-143). Per-request state of fixed size lives beside it: one tensor [max_requests, *shape]
@@ -20,11 +21,23 @@ from .manager import GroupSpec
 
 @dataclass(frozen=True)
 class MemberSpec:
-    """What one layer's cache needs: a group (by window) and the size of a token's K or V."""
+    """What one layer's cache needs: a group (by window and kept first tokens) and the sizes of a
+    token's K and V (`v_head_dim` 0: values have the keys' head size)."""
 
     n_kv_heads: int
     head_dim: int
     window: int = 0
+    v_head_dim: int = 0
+    keep_first: int = 0
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_head_dim or self.head_dim
+
+    @property
+    def lifetime(self) -> tuple[int, int]:
+        """Members whose pages live equally long: without a window every position is kept anyway."""
+        return (self.window, self.keep_first if self.window > 0 else 0)
 
 
 @dataclass
@@ -40,20 +53,22 @@ class CacheMember:
     n_kv_heads: int
     head_dim: int
     window: int
+    v_head_dim: int = 0  # 0: the keys' head size
+    keep_first: int = 0
 
 
 def derive_groups(members: list[MemberSpec], page_size: int, num_pages: int) -> tuple[list[GroupSpec], list[int]]:
-    """Members with the same lifetime (here: the same window) share a group
+    """Members with the same lifetime (here: the same window and the same kept first tokens) share a group
     (kelpie-models/kelpie_models/sdk/groups.py:268-294). -> (groups, group index per member)."""
-    keys: list[int] = []
+    keys: list[tuple[int, int]] = []
     index: list[int] = []
     for m in members:
-        if m.window not in keys:
-            keys.append(m.window)
-        index.append(keys.index(m.window))
+        if m.lifetime not in keys:
+            keys.append(m.lifetime)
+        index.append(keys.index(m.lifetime))
     if not keys:  # a model without any per-token cache still gets one (empty) group
-        keys.append(0)
-    return [GroupSpec(page_size, w, num_pages) for w in keys], index
+        keys.append((0, 0))
+    return [GroupSpec(page_size, w, num_pages, keep) for w, keep in keys], index
 
 
 class KVArena:
@@ -64,9 +79,10 @@ class KVArena:
         sizes = [0] * len(groups)
         offsets = []
         for m, g in zip(members, member_group):
-            elems = m.n_kv_heads * groups[g].page_size * m.head_dim
-            offsets.append((sizes[g], sizes[g] + elems))
-            sizes[g] += 2 * elems
+            k_elems = m.n_kv_heads * groups[g].page_size * m.head_dim
+            v_elems = m.n_kv_heads * groups[g].page_size * m.value_dim
+            offsets.append((sizes[g], sizes[g] + k_elems))
+            sizes[g] += k_elems + v_elems
         self.tensors = [
             torch.zeros(groups[g].num_pages + 1, max(sizes[g], 1), dtype=dtype, device=device)
             for g in range(len(groups))
@@ -77,6 +93,7 @@ class KVArena:
             self.members.append(CacheMember(
                 group=g, k=flat[k_off:], v=flat[v_off:], page_stride=sizes[g], page_size=groups[g].page_size,
                 n_pages=groups[g].num_pages + 1, n_kv_heads=m.n_kv_heads, head_dim=m.head_dim, window=m.window,
+                v_head_dim=m.v_head_dim, keep_first=m.keep_first,
             ))
 
     def fill_(self, value: float) -> None:

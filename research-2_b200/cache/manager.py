@@ -39,6 +39,7 @@ class GroupSpec:
     page_size: int
     window: int = 0  # 0 = every position is kept; w > 0 = a query at p reads keys (p - w, p]
     num_pages: int = 1  # pages that can be handed out; page id 0 (the null page) is extra
+    keep_first: int = 0  # with a window: the request's first keep_first positions stay readable as well
 
 
 def _ptr(a: np.ndarray):
@@ -49,7 +50,7 @@ def _ptr(a: np.ndarray):
 def group_array(groups: list[GroupSpec]):
     arr = (_host.GroupSpecC * len(groups))()
     for i, g in enumerate(groups):
-        arr[i] = _host.GroupSpecC(g.page_size, g.window, g.num_pages)
+        arr[i] = _host.GroupSpecC(g.page_size, g.window, g.num_pages, g.keep_first)
     return arr
 
 

@@ -69,7 +69,7 @@ def cmd_generate(args) -> int:
 
 def cmd_random(args) -> int:
     from .config.registry import architecture_of
-    from .models import gpt2  # noqa: F401
+    from . import models  # noqa: F401  (registers the architectures)
     from .weights.model_folder import write_model_folder
 
     with open(args.config) as f:

@@ -11,9 +11,10 @@ from .registry import (
 )
 from .engine_options import EngineOptions
 from .gpt2 import GPT2Config
+from .zirunex import ZirunexConfig
 
 __all__ = [
-    "Architecture", "ConfigError", "EngineOptions", "GPT2Config", "architecture", "architecture_of",
+    "Architecture", "ConfigError", "EngineOptions", "GPT2Config", "ZirunexConfig", "architecture", "architecture_of",
     "known_architectures", "load_config", "read_config_json", "register_architecture",
     "unregister_architecture",
 ]

@@ -16,13 +16,15 @@ from .registry import ConfigError
 DTYPES = ("bfloat16", "float32")
 ORDERS = ("running_first", "waiting_first")
 MAX_BUDGET = 8192  # the reference's ceiling for both budgets (kelpie-core/src/c_api.zig:467-478)
+DEFAULT_SEQ_LEN = 4096  # for a model that has no limit of its own (positions enter nothing but its masks)
+UNBOUNDED = 1 << 24  # a model whose own limit is at least this long counts as having none
 
 
 @dataclass(frozen=True)
 class EngineOptions:
     dtype: str = "bfloat16"
     max_requests: int = 8
-    max_seq_len: int = 0  # 0 = the model's own maximum
+    max_seq_len: int = 0  # 0 = the model's own maximum (DEFAULT_SEQ_LEN for a model without one)
     block_size: int = 16  # tokens per cache page
     num_slabs: int = 0  # pages per cache group; 0 = enough for max_requests full sequences
     max_batch_tokens: int = 1024
@@ -42,7 +44,7 @@ class EngineOptions:
             raise ConfigError(f"max_requests must be >= 1, got {self.max_requests}")
         if self.block_size < 1:
             raise ConfigError(f"block_size must be >= 1, got {self.block_size}")
-        max_seq = self.max_seq_len or model_max_seq_len
+        max_seq = self.max_seq_len or (model_max_seq_len if model_max_seq_len < UNBOUNDED else DEFAULT_SEQ_LEN)
         if not 1 <= max_seq <= model_max_seq_len:
             raise ConfigError(
                 f"max_seq_len must be in [1, {model_max_seq_len}] (the model's limit), got {max_seq}"

@@ -1,4 +1,4 @@
-"""One registry from an architecture's name (config.json `architectures[0]`) to its model.
+"""One registry from an architecture's name (config.json `architectures[0]` or `architecture`) to its model.
 
 An architecture is four functions, and nothing else in the package knows a model by name:
 
@@ -63,11 +63,15 @@ def architecture(name: str) -> Architecture:
 
 
 def architecture_of(config_json: dict) -> Architecture:
-    """The architecture that a config.json names in `architectures`."""
+    """The architecture that a config.json names: one name in the list `architectures`, or the
+    plain string `architecture`."""
+    single = config_json.get("architecture")
+    if isinstance(single, str) and "architectures" not in config_json:
+        return architecture(single)
     names = config_json.get("architectures")
     if not isinstance(names, list) or len(names) != 1 or not isinstance(names[0], str):
         raise ConfigError(
-            f"config.json must name exactly one model in 'architectures', got {names!r}; "
+            f"config.json must name exactly one model in 'architectures' (or 'architecture'), got {names!r}; "
             f"known: {', '.join(known_architectures())}"
         )
     return architecture(names[0])

@@ -24,6 +24,7 @@ static bool groups_ok(const R2GroupSpec* groups, int32_t n_groups, int32_t max_r
   for (int32_t g = 0; g < n_groups; ++g) {
     if (groups[g].page_size < 1) { g_error = "group " + std::to_string(g) + ": page_size must be >= 1"; return false; }
     if (groups[g].window < 0) { g_error = "group " + std::to_string(g) + ": window must be >= 0"; return false; }
+    if (groups[g].keep_first < 0) { g_error = "group " + std::to_string(g) + ": keep_first must be >= 0"; return false; }
     if (groups[g].num_pages < 1) { g_error = "group " + std::to_string(g) + ": num_pages must be >= 1"; return false; }
   }
   return true;
@@ -31,7 +32,7 @@ static bool groups_ok(const R2GroupSpec* groups, int32_t n_groups, int32_t max_r
 
 static std::vector<r2::GroupSpec> to_groups(const R2GroupSpec* groups, int32_t n) {
   std::vector<r2::GroupSpec> out;
-  for (int32_t g = 0; g < n; ++g) out.push_back({groups[g].page_size, groups[g].window, groups[g].num_pages});
+  for (int32_t g = 0; g < n; ++g) out.push_back({groups[g].page_size, groups[g].window, groups[g].num_pages, groups[g].keep_first});
   return out;
 }
 

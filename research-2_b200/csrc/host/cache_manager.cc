@@ -66,11 +66,17 @@ int32_t CacheManager::first_needed_page(int32_t g, int32_t n_computed) const {
   return first_key / spec.page_size;
 }
 
+int32_t CacheManager::kept_pages(int32_t g) const {
+  const GroupSpec& spec = groups_[g];
+  if (spec.window <= 0 || spec.keep_first <= 0) return 0;
+  return ceil_div(spec.keep_first, spec.page_size);
+}
+
 int32_t CacheManager::pages_to_take(int32_t req, int32_t g, int32_t n_computed, int32_t n_total) const {
   const int32_t* t = table(req, g);
   int32_t end = ceil_div(n_total, groups_[g].page_size);
   int32_t need = 0;
-  for (int32_t i = first_needed_page(g, n_computed); i < end; ++i) need += (t[i] == 0);
+  for (int32_t i = 0; i < end; ++i) need += (needed(g, i, n_computed) && t[i] == 0);
   return need;
 }
 
@@ -91,8 +97,8 @@ int32_t CacheManager::reserve(int32_t req, int32_t n_computed, int32_t n_total) 
   for (int32_t g = 0; g < n_groups(); ++g) {
     int32_t* t = &tables_[g][size_t(req) * widths_[g]];
     int32_t end = ceil_div(n_total, groups_[g].page_size);
-    for (int32_t i = first_needed_page(g, n_computed); i < end; ++i) {
-      if (t[i] == 0) {
+    for (int32_t i = 0; i < end; ++i) {
+      if (needed(g, i, n_computed) && t[i] == 0) {
         t[i] = pools_[g].take();
         held_count_[g][req] += 1;
       }
@@ -107,7 +113,7 @@ int32_t CacheManager::slide(int32_t req, int32_t n_computed) {
     if (groups_[g].window <= 0) continue;
     int32_t* t = &tables_[g][size_t(req) * widths_[g]];
     int32_t first = std::min(first_needed_page(g, n_computed), widths_[g]);
-    for (int32_t i = 0; i < first; ++i) {
+    for (int32_t i = kept_pages(g); i < first; ++i) {
       if (t[i] != 0) {
         pools_[g].give(t[i]);
         t[i] = 0;
@@ -125,9 +131,11 @@ int32_t CacheManager::worst_pages(int32_t g, int32_t n_total, int32_t max_chunk,
   // A portion of rows [s, e) needs the keys from s - window + 1 up to e - 1. Portions are
   // either one decoded row at any s, or a piece of a history: it starts on a multiple of
   // `grain` and ends on one unless it reaches the history's end. The most pages over all of them:
+  // (kept first pages that lie before the window's first page come on top)
   int32_t worst = 0;
   max_chunk = std::max(1, max_chunk);
   grain = std::max(1, grain);
+  const int32_t kept = kept_pages(g);
   for (int32_t s = 0; s < n_total; ++s) {
     int32_t first_page = std::max(0, s - spec.window + 1) / spec.page_size;
     int32_t e = s + 1;  // the single decoded row
@@ -136,7 +144,7 @@ int32_t CacheManager::worst_pages(int32_t g, int32_t n_total, int32_t max_chunk,
       if (e < n_total) e = e / grain * grain;
       if (e <= s) e = s + 1;
     }
-    worst = std::max(worst, (e - 1) / spec.page_size - first_page + 1);
+    worst = std::max(worst, (e - 1) / spec.page_size - first_page + 1 + std::min(kept, first_page));
   }
   return std::min(all, worst);
 }

@@ -3,8 +3,8 @@
 //
 // It owns indices only; the tensors that the indices point into belong to the model side.
 // A cache group is a set of layers whose pages live and die together: "all" groups keep every
-// position of a request, "window" groups keep the last `window` positions and give pages back
-// as soon as the window has passed them. Every group has a pool of its own. Page id 0 of each
+// position of a request, "window" groups keep the last `window` positions (and, with `keep_first`,
+// the request's first positions) and give the pages between back as soon as the window has passed them. Every group has a pool of its own. Page id 0 of each
 // pool is the null page: real memory that is never handed out; holes in a block table point
 // at it. This restates the block pool of the reference's core (kelpie-core/src/kv_pool.zig:
 // 17-25,183-188,254-301; block tables kelpie-core/src/request.zig:78-81,218-278) without its
@@ -22,6 +22,7 @@ struct GroupSpec {
   int32_t page_size;  // tokens per page
   int32_t window;     // 0: keep every position; w > 0: a query at p reads keys (p - w, p]
   int32_t num_pages;  // pages that can be handed out (the null page is extra)
+  int32_t keep_first; // with a window: the request's first keep_first positions stay readable for good
 };
 
 // One group's pages. Freed pages are reused in the order in which they were freed.
@@ -65,8 +66,12 @@ class CacheManager {
   // Every page of the request goes back to its pool; the state slot is released.
   int32_t close(int32_t req);
 
-  // First page index that group g still needs when the request's next row is at `n_computed`.
+  // First page index that group g's window still needs when the request's next row is at `n_computed`.
   int32_t first_needed_page(int32_t g, int32_t n_computed) const;
+  // Pages at a table's start that hold kept first positions and are never given back while the request lives.
+  int32_t kept_pages(int32_t g) const;
+  // Whether page index i of group g is needed by a request whose next row is at n_computed.
+  bool needed(int32_t g, int32_t i, int32_t n_computed) const { return i < kept_pages(g) || i >= first_needed_page(g, n_computed); }
   // Pages that group g must take so that the request holds positions up to n_total (exclusive),
   // given that its next row is at n_computed.
   int32_t pages_to_take(int32_t req, int32_t g, int32_t n_computed, int32_t n_total) const;

@@ -13,12 +13,13 @@
 extern "C" {
 #endif
 
-#define R2_ABI_VERSION 4
+#define R2_ABI_VERSION 5
 
 typedef struct {
   int32_t page_size;
   int32_t window;
   int32_t num_pages;
+  int32_t keep_first; /* with a window: a request's first keep_first positions are kept for good */
 } R2GroupSpec;
 
 typedef struct {

@@ -310,7 +310,8 @@ void Scheduler::detect_stall(bool preempted) {
   // the group that is shortest of pages for this portion
   int32_t worst = 0, worst_gap = 0;
   for (int32_t g = 0; g < cache_.n_groups(); ++g) {
-    int32_t need = ceil_div(r.n_computed + stall_.n_work, cache_.group(g).page_size) - cache_.first_needed_page(g, r.n_computed);
+    const int32_t first_page = cache_.first_needed_page(g, r.n_computed);
+    int32_t need = ceil_div(r.n_computed + stall_.n_work, cache_.group(g).page_size) - first_page + std::min(cache_.kept_pages(g), first_page);
     if (cache_.is_open(id)) need = cache_.pages_to_take(id, g, r.n_computed, r.n_computed + stall_.n_work);
     if (stall_.n_work == 0) need = 0;
     int32_t gap = need - cache_.n_free(g);

@@ -3,12 +3,12 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------------------------------------
-// x[t] = table[ids[t]] (+ pos_table[positions[t]]), written as float (the residual stream).
+// x[t] = table[ids[t]] * scale (+ pos_table[positions[t]]), written as float (the residual stream).
 // Reference: kelpie-models/kelpie_models/models/torch/gpt2.py:90.
 template <typename W>
 __global__ void embed_kernel(const int32_t* __restrict__ ids, const int32_t* __restrict__ positions,
                              const W* __restrict__ table, const W* __restrict__ pos_table,
-                             float* __restrict__ out, int width, int n_vocab, int n_positions) {
+                             float* __restrict__ out, int width, int n_vocab, int n_positions, float scale) {
   pdl_launch_dependents();  // the next kernel may begin its prologue
   pdl_wait();               // the previous kernel's writes are visible from here on
   int t = blockIdx.x;
@@ -23,24 +23,24 @@ __global__ void embed_kernel(const int32_t* __restrict__ ids, const int32_t* __r
   }
   float* o = out + size_t(t) * width;
   for (int d = threadIdx.x; d < width; d += blockDim.x) {
-    float v = to_float(row[d]);
+    float v = to_float(row[d]) * scale;
     if (prow != nullptr) v += to_float(prow[d]);
     o[d] = v;
   }
 }
 
 extern "C" int r2_embed(const int32_t* ids, const int32_t* positions, const void* table, const void* pos_table,
-                        float* out, int n_rows, int width, int n_vocab, int n_positions, int wdtype,
+                        float* out, int n_rows, int width, int n_vocab, int n_positions, int wdtype, float scale,
                         cudaStream_t stream) {
   if (n_rows <= 0) return R2_OK;
   if (width < 1 || n_vocab < 1) return R2_BAD_SHAPE;
   int threads = width >= 256 ? 256 : (width >= 128 ? 128 : 64);
   if (wdtype == R2_F32) {
     r2_launch(embed_kernel<float>, dim3(n_rows), dim3(threads), size_t(0), stream, ids, positions, (const float*)table, (const float*)pos_table,
-                                                        out, width, n_vocab, n_positions);
+                                                        out, width, n_vocab, n_positions, scale);
   } else if (wdtype == R2_BF16) {
     r2_launch(embed_kernel<bf16>, dim3(n_rows), dim3(threads), size_t(0), stream, ids, positions, (const bf16*)table, (const bf16*)pos_table,
-                                                       out, width, n_vocab, n_positions);
+                                                       out, width, n_vocab, n_positions, scale);
   } else {
     return R2_BAD_DTYPE;
   }
@@ -167,11 +167,11 @@ extern "C" int r2_layer_norm(const float* x, const int32_t* rows, const float* g
 // Keys and values of this step's rows go to their cache slots before attention reads them
 // (kelpie-models/kelpie_models/kernels/ops/paged_attention.py:44-53). A slot is
 // page * page_size + offset; inside a page the layout is [kv_head][offset][head_dim], and a
-// page of this layer starts every `page_stride` elements.
+// page of this layer starts every `page_stride` elements. Values may have a head size of their own.
 template <typename A, typename C>
 __global__ void kv_write_kernel(const A* __restrict__ k_src, const A* __restrict__ v_src, int src_row_stride,
                                 C* __restrict__ k_cache, C* __restrict__ v_cache,
-                                const int32_t* __restrict__ slot_mapping, int n_kv_heads, int head_dim,
+                                const int32_t* __restrict__ slot_mapping, int n_kv_heads, int head_dim, int v_head_dim,
                                 int page_size, long long page_stride, int n_pages) {
   pdl_launch_dependents();  // the next kernel may begin its prologue
   pdl_wait();               // the previous kernel's writes are visible from here on
@@ -179,32 +179,149 @@ __global__ void kv_write_kernel(const A* __restrict__ k_src, const A* __restrict
   int slot = slot_mapping[t];
   int page = slot / page_size, off = slot % page_size;
   if (slot < 0 || page >= n_pages) return;  // slots are validated on the host; never write outside the pool
-  int width = n_kv_heads * head_dim;
   const A* ks = k_src + size_t(t) * src_row_stride;
   const A* vs = v_src + size_t(t) * src_row_stride;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+  for (int i = threadIdx.x; i < n_kv_heads * head_dim; i += blockDim.x) {
     int h = i / head_dim, d = i % head_dim;
-    size_t dst = size_t(page) * page_stride + (size_t(h) * page_size + off) * head_dim + d;
-    k_cache[dst] = from_float<C>(to_float(ks[i]));
-    v_cache[dst] = from_float<C>(to_float(vs[i]));
+    k_cache[size_t(page) * page_stride + (size_t(h) * page_size + off) * head_dim + d] = from_float<C>(to_float(ks[i]));
+  }
+  for (int i = threadIdx.x; i < n_kv_heads * v_head_dim; i += blockDim.x) {
+    int h = i / v_head_dim, d = i % v_head_dim;
+    v_cache[size_t(page) * page_stride + (size_t(h) * page_size + off) * v_head_dim + d] = from_float<C>(to_float(vs[i]));
   }
 }
 
 extern "C" int r2_kv_write(const void* k_src, const void* v_src, int src_row_stride, void* k_cache, void* v_cache,
-                           const int32_t* slot_mapping, int n_rows, int n_kv_heads, int head_dim, int page_size,
+                           const int32_t* slot_mapping, int n_rows, int n_kv_heads, int head_dim, int v_head_dim, int page_size,
                            long long page_stride, int n_pages_total, int dtype, cudaStream_t stream) {
   if (n_rows <= 0) return R2_OK;
-  if (n_kv_heads < 1 || head_dim < 1 || page_size < 1 || n_pages_total < 1) return R2_BAD_SHAPE;
-  int width = n_kv_heads * head_dim;
+  if (n_kv_heads < 1 || head_dim < 1 || v_head_dim < 1 || page_size < 1 || n_pages_total < 1) return R2_BAD_SHAPE;
+  int width = n_kv_heads * (head_dim > v_head_dim ? head_dim : v_head_dim);
   int threads = width >= 256 ? 256 : 128;
   if (dtype == R2_F32) {
     r2_launch(kv_write_kernel<float, float>, dim3(n_rows), dim3(threads), size_t(0), stream, (const float*)k_src, (const float*)v_src, src_row_stride,
                                                                   (float*)k_cache, (float*)v_cache, slot_mapping,
-                                                                  n_kv_heads, head_dim, page_size, page_stride, n_pages_total);
+                                                                  n_kv_heads, head_dim, v_head_dim, page_size, page_stride, n_pages_total);
   } else if (dtype == R2_BF16) {
     r2_launch(kv_write_kernel<bf16, bf16>, dim3(n_rows), dim3(threads), size_t(0), stream, (const bf16*)k_src, (const bf16*)v_src, src_row_stride,
                                                                 (bf16*)k_cache, (bf16*)v_cache, slot_mapping,
-                                                                n_kv_heads, head_dim, page_size, page_stride, n_pages_total);
+                                                                n_kv_heads, head_dim, v_head_dim, page_size, page_stride, n_pages_total);
+  } else {
+    return R2_BAD_DTYPE;
+  }
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------
+// RMS norm: y = x / sqrt(mean(x^2) + eps) * (offset + w), statistics in float. `offset` is 1 for a
+// weight that is stored around zero and 0 for a plain gain. `rows` (may be null) picks input rows.
+// One warp per row, the row read twice (the second pass comes from L1/L2).
+template <typename O>
+__global__ void __launch_bounds__(128)
+rms_norm_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows, const float* __restrict__ weight,
+                O* __restrict__ out, int n_rows, int width, float eps, float offset) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (r >= n_rows) return;
+  const int src = rows != nullptr ? rows[r] : r;
+  const float* xr = x + size_t(src) * width;
+  float sq = 0.f;
+  for (int d = lane; d < width; d += 32) {
+    float v = xr[d];
+    sq = fmaf(v, v, sq);
+  }
+  const float inv = 1.f / sqrtf(warp_sum(sq) / float(width) + eps);
+  O* o = out + size_t(r) * width;
+  for (int d = lane; d < width; d += 32) o[d] = from_float<O>(xr[d] * inv * (offset + weight[d]));
+}
+
+extern "C" int r2_rms_norm(const float* x, const int32_t* rows, const float* weight, void* out, int n_rows, int width,
+                           float eps, float offset, int odtype, cudaStream_t stream) {
+  if (n_rows <= 0) return R2_OK;
+  if (width < 1) return R2_BAD_SHAPE;
+  dim3 grid((n_rows + 3) / 4);
+  if (odtype == R2_F32) {
+    r2_launch(rms_norm_kernel<float>, grid, dim3(128), size_t(0), stream, x, rows, weight, (float*)out, n_rows, width, eps, offset);
+  } else if (odtype == R2_BF16) {
+    r2_launch(rms_norm_kernel<bf16>, grid, dim3(128), size_t(0), stream, x, rows, weight, (bf16*)out, n_rows, width, eps, offset);
+  } else {
+    return R2_BAD_DTYPE;
+  }
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------
+// RMS norm of every head of the query and key columns of a fused projection, in place: the row's
+// first n_q_heads heads take the gain w_q, the n_k_heads heads after them w_k (both of head_dim
+// values, shared by all heads of their kind). One warp per (row, head), sums in float.
+template <typename T>
+__global__ void __launch_bounds__(128)
+head_norm_kernel(T* __restrict__ buf, int row_stride, int n_rows, int n_q_heads, int n_k_heads, int head_dim,
+                 const float* __restrict__ w_q, const float* __restrict__ w_k, float eps, float offset) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int heads = n_q_heads + n_k_heads;
+  const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (item >= (long long)n_rows * heads) return;
+  const int r = int(item / heads), h = int(item % heads);
+  T* p = buf + size_t(r) * row_stride + size_t(h) * head_dim;
+  const float* w = h < n_q_heads ? w_q : w_k;
+  float sq = 0.f;
+  for (int d = lane; d < head_dim; d += 32) {
+    float v = to_float(p[d]);
+    sq = fmaf(v, v, sq);
+  }
+  const float inv = 1.f / sqrtf(warp_sum(sq) / float(head_dim) + eps);
+  for (int d = lane; d < head_dim; d += 32) p[d] = from_float<T>(to_float(p[d]) * inv * (offset + w[d]));
+}
+
+extern "C" int r2_head_norm(void* buf, int row_stride, int n_rows, int n_q_heads, int n_k_heads, int head_dim,
+                            const float* w_q, const float* w_k, float eps, float offset, int dtype, cudaStream_t stream) {
+  if (n_rows <= 0) return R2_OK;
+  if (n_q_heads < 0 || n_k_heads < 0 || n_q_heads + n_k_heads < 1 || head_dim < 1) return R2_BAD_SHAPE;
+  const long long items = (long long)n_rows * (n_q_heads + n_k_heads);
+  dim3 grid((unsigned)((items + 3) / 4));
+  if (dtype == R2_F32) {
+    r2_launch(head_norm_kernel<float>, grid, dim3(128), size_t(0), stream, (float*)buf, row_stride, n_rows, n_q_heads, n_k_heads, head_dim, w_q, w_k, eps, offset);
+  } else if (dtype == R2_BF16) {
+    r2_launch(head_norm_kernel<bf16>, grid, dim3(128), size_t(0), stream, (bf16*)buf, row_stride, n_rows, n_q_heads, n_k_heads, head_dim, w_q, w_k, eps, offset);
+  } else {
+    return R2_BAD_DTYPE;
+  }
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------
+// The inner activation of a gated feed-forward whose two projections are clamped:
+//   g = min(gate, limit), u = clamp(up, -limit, limit), y = g * sigmoid(alpha * g) * (u + up_offset).
+// `gate_up` holds a row's gate values in columns [0, inner) and its up values in [inner, 2 inner).
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_act_kernel(const T* __restrict__ gate_up, int in_stride, T* __restrict__ out, int out_stride, int inner,
+                 float limit, float alpha, float up_offset) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const T* in = gate_up + size_t(blockIdx.x) * in_stride;
+  T* o = out + size_t(blockIdx.x) * out_stride;
+  for (int f = blockIdx.y * blockDim.x + threadIdx.x; f < inner; f += gridDim.y * blockDim.x) {
+    float g = fminf(to_float(in[f]), limit);
+    float u = fminf(fmaxf(to_float(in[inner + f]), -limit), limit);
+    o[f] = from_float<T>(g / (1.f + expf(-alpha * g)) * (u + up_offset));
+  }
+}
+
+extern "C" int r2_gated_act(const void* gate_up, int in_stride, void* out, int out_stride, int n_rows, int inner, float limit,
+                            float alpha, float up_offset, int dtype, cudaStream_t stream) {
+  if (n_rows <= 0) return R2_OK;
+  if (inner < 1) return R2_BAD_SHAPE;
+  dim3 grid(n_rows, (inner + 1023) / 1024);
+  if (dtype == R2_F32) {
+    r2_launch(gated_act_kernel<float>, grid, dim3(256), size_t(0), stream, (const float*)gate_up, in_stride, (float*)out, out_stride, inner, limit, alpha, up_offset);
+  } else if (dtype == R2_BF16) {
+    r2_launch(gated_act_kernel<bf16>, grid, dim3(256), size_t(0), stream, (const bf16*)gate_up, in_stride, (bf16*)out, out_stride, inner, limit, alpha, up_offset);
   } else {
     return R2_BAD_DTYPE;
   }

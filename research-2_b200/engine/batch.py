@@ -197,7 +197,7 @@ class BatchLimits:
         from ..cache import _host
 
         self.vocab_size, self.max_seq_len, self.n_groups = int(vocab_size), int(max_seq_len), len(groups)
-        self.groups = (_host.GroupSpecC * len(groups))(*[_host.GroupSpecC(g.page_size, g.window, g.num_pages) for g in groups])
+        self.groups = (_host.GroupSpecC * len(groups))(*[_host.GroupSpecC(g.page_size, g.window, g.num_pages, g.keep_first) for g in groups])
         self.table_widths = (C.c_int32 * len(groups))(*[int(w) for w in table_widths])
 
 

@@ -34,7 +34,8 @@ class Engine:
         from .step import StepFunction
 
         opts = (options or EngineOptions()).validated(model.max_seq_len)
-        step_fn = StepFunction(model, opts.block_size, opts.num_slabs, opts.max_requests, capture=bool(opts.capture))
+        step_fn = StepFunction(model, opts.block_size, opts.num_slabs, opts.max_requests, capture=bool(opts.capture),
+                               max_seq_len=opts.max_seq_len)
         scheduler = Scheduler(
             SchedulerConfig(
                 max_requests=opts.max_requests, max_seq_len=opts.max_seq_len, max_batch_tokens=opts.max_batch_tokens,

@@ -38,8 +38,11 @@ class Replay:
             raise ValueError("block size, live requests and rounding must be >= 1")
         self.model = load_model(model_dir, dtype=dtype, device=device)
         num_pages = -(-max_tokens // block_size) + (max_live if round_to % block_size else 0)
-        self.step_fn = StepFunction(self.model, block_size, num_pages, max_live, capture=capture, capture_after=0)
-        self.cache = CacheManager(self.step_fn.cache_groups(), max_live, self.model.max_seq_len)
+        # no request holds more than the pool: a model without a length limit of its own is run up to there
+        longest = min(self.model.max_seq_len, -(-max_tokens // round_to) * round_to)
+        self.step_fn = StepFunction(self.model, block_size, num_pages, max_live, capture=capture, capture_after=0,
+                                    max_seq_len=longest)
+        self.cache = CacheManager(self.step_fn.cache_groups(), max_live, self.step_fn.max_seq_len)
         self.slots: dict[str, int] = {}
         self.fed: dict[str, int] = {}
         self.max_live = max_live

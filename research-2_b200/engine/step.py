@@ -95,7 +95,7 @@ class StepGraph:
         self.cap = r_cap
         self.device = step_fn.device
         self.host = StepBatch(BatchLayout(t_cap, r_cap, r_cap, step_fn.table_widths), pinned=True)
-        self.host.max_context_bound = step_fn.model.max_seq_len
+        self.host.max_context_bound = step_fn.max_seq_len
         self.host.pad()
         self.host.set_logit_rows([])
         self.host.set_sampling([], [], [], [], [])
@@ -162,11 +162,13 @@ class StepGraph:
 
 class StepFunction:
     def __init__(self, model, page_size: int, num_pages: int, max_requests: int, capture: bool = False,
-                 capture_after: int = 1):
+                 capture_after: int = 1, max_seq_len: int = 0):
         """`capture`: steps run as CUDA graphs per shape bucket. A decode-only bucket is captured at
         first use; a bucket with prompt portions once its shape has come `capture_after` times
-        before (0: at first use)."""
+        before (0: at first use). `max_seq_len` (0: the model's own) is the longest sequence that the
+        cache manager beside this step function admits; block tables are as wide as it needs."""
         self.model = model
+        self.max_seq_len = min(max_seq_len, model.max_seq_len) if max_seq_len > 0 else model.max_seq_len
         self.device = model.rt.device
         # the device's number, for the launch path that skips torch's device guard when it is the current one
         self._device_index = self.device.index if self.device.index is not None else (torch.cuda.current_device() if torch.cuda.is_available() else 0)
@@ -177,8 +179,8 @@ class StepFunction:
             for spec in model.state_members
         ]
         self.max_requests = max_requests
-        self.table_widths = tuple(-(-model.max_seq_len // g.page_size) for g in self.groups)
-        self._limits = BatchLimits(model.vocab_size, model.max_seq_len, self.groups, self.table_widths)
+        self.table_widths = tuple(-(-self.max_seq_len // g.page_size) for g in self.groups)
+        self._limits = BatchLimits(model.vocab_size, self.max_seq_len, self.groups, self.table_widths)
         # A mixer with state of its own folds an entry's rows on the host side of the launch, so
         # only models whose mixers all say `capturable` may run inside a CUDA graph.
         self.capture = capture and all(getattr(b.mixer, "capturable", False) for b in model.blocks)

@@ -347,8 +347,8 @@ def wait_selftest(device="cuda:0", polls: int = 64, code: int = 99) -> None:
 
 
 def embed(ids: torch.Tensor, table: torch.Tensor, positions: torch.Tensor | None = None,
-          pos_table: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
-    """out[t] = table[ids[t]] (+ pos_table[positions[t]]) as float32 [T, width]."""
+          pos_table: torch.Tensor | None = None, out: torch.Tensor | None = None, scale: float = 1.0) -> torch.Tensor:
+    """out[t] = table[ids[t]] * scale (+ pos_table[positions[t]]) as float32 [T, width]."""
     _need(ids, "ids", torch.int32, 1)
     _need(table, "table", dim=2)
     n, width = ids.shape[0], table.shape[1]
@@ -364,7 +364,7 @@ def embed(ids: torch.Tensor, table: torch.Tensor, positions: torch.Tensor | None
     _need(out, "out", torch.float32, 2)
     fn = _lib("rowwise").r2_embed
     status = fn(_p(ids), _p(positions), _p(table), _p(pos_table), _p(out), n, width, table.shape[0],
-                0 if pos_table is None else pos_table.shape[0], dtype_code(table.dtype), _stream())
+                0 if pos_table is None else pos_table.shape[0], dtype_code(table.dtype), C.c_float(scale), _stream())
     _check(status, "embed")
     return out
 
@@ -386,6 +386,58 @@ def layer_norm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: fl
     status = _lib("rowwise").r2_layer_norm(_p(x), _p(rows), _p(gamma), _p(beta), _p(out), n, x.shape[1],
                                           C.c_float(eps), dtype_code(out.dtype), _stream())
     _check(status, "layer_norm")
+    return out
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype, rows: torch.Tensor | None = None,
+             unit_offset: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:
+    """x / sqrt(mean(x^2) + eps) * w of float32 rows, statistics in float32; with `unit_offset` the gain is
+    1 + w (a weight stored around zero). `rows` (int32) picks input rows, else all rows in order."""
+    _need(x, "x", torch.float32, 2)
+    _need(weight, "weight", torch.float32, 1)
+    if not x.is_contiguous() or weight.shape[0] != x.shape[1]:
+        raise KernelError(f"rms_norm: x {tuple(x.shape)} weight {tuple(weight.shape)}")
+    n = x.shape[0]
+    if rows is not None:
+        _need(rows, "rows", torch.int32, 1)
+        n = rows.shape[0]
+    if out is None:
+        out = torch.empty(n, x.shape[1], dtype=out_dtype, device=x.device)
+    status = _lib("rowwise").r2_rms_norm(_p(x), _p(rows), _p(weight), _p(out), n, x.shape[1], C.c_float(eps),
+                                        C.c_float(1.0 if unit_offset else 0.0), dtype_code(out.dtype), _stream())
+    _check(status, "rms_norm")
+    return out
+
+
+def head_norm(buf: torch.Tensor, n_q_heads: int, n_k_heads: int, head_dim: int, w_q: torch.Tensor, w_k: torch.Tensor,
+              eps: float, unit_offset: bool = False) -> None:
+    """RMS norm, in place, of each of the first n_q_heads + n_k_heads heads of every row of `buf` (a fused
+    projection whose first columns are the query heads and then the key heads); the query heads take the
+    gain `w_q`, the key heads `w_k` (float32 [head_dim], shared by the heads of a kind)."""
+    _need(buf, "buf", dim=2)
+    _need(w_q, "w_q", torch.float32, 1)
+    _need(w_k, "w_k", torch.float32, 1)
+    if w_q.shape[0] != head_dim or w_k.shape[0] != head_dim or buf.shape[1] < (n_q_heads + n_k_heads) * head_dim:
+        raise KernelError(f"head_norm: buf {tuple(buf.shape)} does not hold {n_q_heads} + {n_k_heads} heads of {head_dim}")
+    status = _lib("rowwise").r2_head_norm(_p(buf), _rows(buf, "buf"), buf.shape[0], n_q_heads, n_k_heads, head_dim, _p(w_q),
+                                         _p(w_k), C.c_float(eps), C.c_float(1.0 if unit_offset else 0.0),
+                                         dtype_code(buf.dtype), _stream())
+    _check(status, "head_norm")
+
+
+def gated_act(gate_up: torch.Tensor, limit: float, alpha: float, up_offset: float, out: torch.Tensor | None = None) -> torch.Tensor:
+    """y = g * sigmoid(alpha * g) * (u + up_offset) with g = min(gate, limit) and u = clamp(up, -limit, limit);
+    a row of `gate_up` [T, 2 F] holds its gate values and then its up values. -> [T, F] in the same dtype."""
+    _need(gate_up, "gate_up", dim=2)
+    if gate_up.shape[1] % 2:
+        raise KernelError(f"gated_act: {tuple(gate_up.shape)} does not hold a gate and an up half")
+    inner = gate_up.shape[1] // 2
+    if out is None:
+        out = torch.empty(gate_up.shape[0], inner, dtype=gate_up.dtype, device=gate_up.device)
+    status = _lib("rowwise").r2_gated_act(_p(gate_up), _rows(gate_up, "gate_up"), _p(out), _rows(out, "out"), gate_up.shape[0],
+                                         inner, C.c_float(limit), C.c_float(alpha), C.c_float(up_offset),
+                                         dtype_code(gate_up.dtype), _stream())
+    _check(status, "gated_act")
     return out
 
 
@@ -547,21 +599,24 @@ def _linear_kv(a: torch.Tensor, w: torch.Tensor, bias, w_is_nk: bool, out, kv: K
 
 def kv_write(k_src: torch.Tensor, v_src: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
              slot_mapping: torch.Tensor, n_kv_heads: int, head_dim: int, page_size: int, page_stride: int,
-             n_pages: int) -> None:
-    """Scatter this step's keys and values [T, n_kv_heads * head_dim] into their cache slots."""
+             n_pages: int, v_head_dim: int = 0) -> None:
+    """Scatter this step's keys [T, n_kv_heads * head_dim] and values [T, n_kv_heads * v_head_dim] (0: the keys'
+    head size) into their cache slots."""
+    v_head_dim = v_head_dim or head_dim
     _need(k_src, "k_src", dim=2)
     _need(v_src, "v_src", k_src.dtype, 2)
     _need(slot_mapping, "slot_mapping", torch.int32, 1)
     if k_cache.dtype != k_src.dtype or v_cache.dtype != k_src.dtype:
         raise KernelError("kv_write: the cache and the new keys/values must share a dtype")
     n = k_src.shape[0]
-    if k_src.shape[1] != n_kv_heads * head_dim or v_src.shape != k_src.shape or slot_mapping.shape[0] < n:
+    if (k_src.shape[1] != n_kv_heads * head_dim or v_src.shape[1] != n_kv_heads * v_head_dim or v_src.shape[0] != n
+            or slot_mapping.shape[0] < n):
         raise KernelError("kv_write: shapes do not fit")
     stride = _rows(k_src, "k_src")
     if _rows(v_src, "v_src") != stride:
         raise KernelError("kv_write: k and v must share a row stride")
     status = _lib("rowwise").r2_kv_write(_p(k_src), _p(v_src), stride, _p(k_cache), _p(v_cache), _p(slot_mapping), n,
-                                        n_kv_heads, head_dim, page_size, C.c_longlong(page_stride), n_pages,
+                                        n_kv_heads, head_dim, v_head_dim, page_size, C.c_longlong(page_stride), n_pages,
                                         dtype_code(k_src.dtype), _stream())
     _check(status, "kv_write")
 
@@ -570,8 +625,12 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                     n_pages: int, block_tables: torch.Tensor, row_entry: torch.Tensor, positions: torch.Tensor,
                     seq_lens: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
                     window: int = 0, out: torch.Tensor | None = None, *, decode_only: bool = False,
-                    max_context: int = 0, q_start: torch.Tensor | None = None, n_tiles: int = 0) -> torch.Tensor:
-    """Causal attention of q [T, n_heads * head_dim] over the paged cache -> [T, n_heads * head_dim].
+                    max_context: int = 0, q_start: torch.Tensor | None = None, n_tiles: int = 0, v_head_dim: int = 0,
+                    keep_first: int = 0, sink: bool = False, gate: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal attention of q [T, n_heads * head_dim] over the paged cache -> [T, n_heads * v_head_dim]
+    (`v_head_dim` 0: the keys' head size). With a window, `keep_first` keeps a sequence's first keys visible;
+    `sink` adds one to the softmax's denominator (a key of score 0 that has no value); `gate`
+    [T, n_heads * v_head_dim] multiplies the output by its sigmoid.
     `decode_only` says that every row is an entry of its own (one new token each) and
     `max_context` bounds the rows' context lengths; `q_start` (int32 [R + 1]) with `n_tiles`, the
     sum over entries of ceil(rows / 64), lets the tensor-core prefill kernel take the batch. They
@@ -587,12 +646,20 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         raise KernelError(f"attention: q {tuple(q.shape)} is not [T, {n_heads} * {head_dim}]")
     if k_cache.dtype != q.dtype or v_cache.dtype != q.dtype:
         raise KernelError("attention: q and the cache must share a dtype")
-    if head_dim % 16 != 0:
-        raise KernelError(f"attention: head sizes come in steps of 16, got {head_dim}")
+    v_head_dim = v_head_dim or head_dim
     if out is None:
-        out = torch.empty(n, n_heads * head_dim, dtype=q.dtype, device=q.device)
+        out = torch.empty(n, n_heads * v_head_dim, dtype=q.dtype, device=q.device)
+    gate_stride = 0
+    if gate is not None:
+        _need(gate, "gate", q.dtype, 2)
+        if gate.shape != (n, n_heads * v_head_dim):
+            raise KernelError(f"attention: gate {tuple(gate.shape)} is not [T, {n_heads} * {v_head_dim}]")
+        gate_stride = _rows(gate, "gate")
     group = n_heads // max(n_kv_heads, 1)
-    if q.dtype == torch.bfloat16 and decode_only and _fast_attention and group in (1, 2, 4, 8):
+    # what only the general kernel takes: a value head size of its own, kept first keys, a sink, an output gate,
+    # or a head size that is no multiple of 16
+    plain = v_head_dim == head_dim and keep_first == 0 and not sink and gate is None and head_dim % 16 == 0
+    if plain and q.dtype == torch.bfloat16 and decode_only and _fast_attention and group in (1, 2, 4, 8):
         lib = _lib_for_head_dim("attention_decode", head_dim)
         n_slices = decode_slices(n, n_kv_heads, max_context, q.device)
         ws = _workspace(q.device)
@@ -608,7 +675,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         if n_slices > 1:
             count_launches(1)  # the merge kernel
         return out
-    if q.dtype == torch.bfloat16 and _fast_attention and _prefill_tc and q_start is not None and n_tiles > 0 and head_dim == 64:
+    if plain and q.dtype == torch.bfloat16 and _fast_attention and _prefill_tc and q_start is not None and n_tiles > 0 and head_dim == 64:
         # tcgen05 form (head size 64, pages of 8, 16, 32 or a multiple of 64 keys): 128-row tiles, one entry to a
         # tile. Also where most tiles are mostly empty (single decoded tokens beside a portion: 64 such rows
         # and 448 of a prompt take 40 us against the mma.sync kernel's 49).
@@ -622,7 +689,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
             _check(status, "paged_attention (prefill, tcgen05)")
             _used("attention_prefill_tc")
             return out
-    if (q.dtype == torch.bfloat16 and _fast_attention and q_start is not None and n_tiles > 0 and head_dim <= 128
+    if (plain and q.dtype == torch.bfloat16 and _fast_attention and q_start is not None and n_tiles > 0 and head_dim <= 128
             and _rows(q, "q") % 8 == 0 and q.data_ptr() % 16 == 0):
         _need(q_start, "q_start", torch.int32, 1)
         lib = _lib_for_head_dim("attention_prefill", head_dim)
@@ -637,8 +704,10 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     status = _lib("attention_simt").r2_attention_simt(
         _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(k_cache), _p(v_cache), C.c_longlong(page_stride),
         page_size, _p(block_tables), block_tables.shape[1], _p(row_entry), _p(positions), _p(seq_lens), n, n_heads,
-        n_kv_heads, head_dim, C.c_float(scale), window, n_pages, dtype_code(q.dtype), _stream())
+        n_kv_heads, head_dim, v_head_dim, C.c_float(scale), window, keep_first, int(bool(sink)), _p(gate), gate_stride,
+        n_pages, dtype_code(q.dtype), _stream())
     _check(status, "paged_attention")
+    _used("attention_simt")
     return out
 
 

@@ -42,6 +42,7 @@ class ModelSpec:
     layers: tuple[LayerSpec, ...]
     final_norm: PartSpec
     schedule: tuple[ScheduleEntry, ...] = field(default=())
+    embedding_scale: float = 1.0  # token table rows are multiplied by it
 
 
 def default_schedule(layers, mixers) -> tuple[ScheduleEntry, ...]:
@@ -62,7 +63,7 @@ class DecoderModel:
         self.spec, self.rt, self.config = spec, rt, config
         self.vocab_size, self.hidden, self.max_seq_len = spec.vocab_size, spec.hidden, spec.max_seq_len
         self.eos_token = spec.eos_token
-        self.embedding = TokenEmbedding(tensors[spec.embedding], rt)
+        self.embedding = TokenEmbedding(tensors[spec.embedding], rt, scale=spec.embedding_scale)
         self.positions = build_part("positions", spec.positions, tensors, rt) if spec.positions else None
         self.blocks = []
         for layer in spec.layers:
@@ -72,8 +73,9 @@ class DecoderModel:
             block_cls = registry("block")[layer.block]
             self.blocks.append(block_cls(
                 build_part("norm", layer.norm_1, tensors, rt), mixer,
-                build_part("norm", layer.norm_2, tensors, rt),
-                build_part("feed_forward", layer.feed_forward, tensors, rt), rt.dtype))
+                build_part("norm", layer.norm_2, tensors, rt) if layer.norm_2 is not None else None,
+                build_part("feed_forward", layer.feed_forward, tensors, rt) if layer.feed_forward is not None else None,
+                rt.dtype))
         mixers = [b.mixer for b in self.blocks]
         self.schedule = spec.schedule or default_schedule(spec.layers, mixers)
         head_table = self.embedding.table if spec.head == spec.embedding else tensors[spec.head].to(rt.device, rt.dtype)
@@ -139,7 +141,7 @@ class DecoderModel:
         add(self.embedding.table if self.head.table.data_ptr() != self.embedding.table.data_ptr() else None)
         add(self.head.table)
         for obj in [self.head.norm] + [p for b in self.blocks for p in (b.norm_1, b.mixer, b.norm_2, b.feed_forward)]:
-            for v in vars(obj).values():
+            for v in (vars(obj).values() if obj is not None else ()):
                 if isinstance(v, torch.Tensor):
                     add(v)
         return total

@@ -93,3 +93,77 @@ class PagedAttention:
             self.window, decode_only=ctx.decode_only, max_context=ctx.max_context, q_start=ctx.q_start,
             n_tiles=ctx.n_attention_tiles)
         return ops.linear(mixed, self.w_out, self.b_out, residual=residual)
+
+
+@register_mixer("qk_norm_attention")
+class QKNormAttention:
+    """Grouped causal attention over the paged cache with an RMS norm of every query and key head, and,
+    each chosen by a parameter: a window that keeps a sequence's first keys, a sink in the softmax's
+    denominator, an output gate, a value head size of its own. No rotation; positions enter the mask only.
+
+    params: n_heads, n_kv_heads, head_dim, v_head_dim, scale, qk_norm_eps, qk_norm_unit_offset (false: the
+    norms' weights are plain gains), window (0 = none; a row at position p reads the keys (p - window, p]),
+    keep_first (with a window: keys at positions below it stay visible), sink (the softmax's denominator is
+    1 + the sum, i.e. one more key of score 0 that has no value).
+    weights, all matrices stored [out, in] and without biases: w_q [H * head_dim, D], w_k [G * head_dim, D],
+    w_v [G * v_head_dim, D], w_out [D, H * v_head_dim], q_norm [head_dim], k_norm [head_dim], and optionally
+    w_gate [H * v_head_dim, D]: the heads' outputs are multiplied by sigmoid(w_gate h) before w_out.
+
+    The projections of one input run as one product over the stacked matrix [q; k; v; gate]; the norms work in
+    place on its query and key columns; keys are cached after their norm."""
+
+    def __init__(self, params: dict, weights: dict, rt: Runtime):
+        self.n_heads, self.n_kv_heads = int(params["n_heads"]), int(params["n_kv_heads"])
+        self.head_dim, self.v_head_dim = int(params["head_dim"]), int(params["v_head_dim"])
+        self.scale = float(params["scale"])
+        self.window, self.keep_first = int(params.get("window", 0)), int(params.get("keep_first", 0))
+        self.sink = bool(params.get("sink", False))
+        self.norm_eps = float(params["qk_norm_eps"])
+        self.norm_unit_offset = bool(params.get("qk_norm_unit_offset", False))
+        if self.n_heads % self.n_kv_heads != 0:
+            raise ValueError(f"attention: n_heads {self.n_heads} is not a multiple of n_kv_heads {self.n_kv_heads}")
+        if not (1 <= self.head_dim <= 256 and 1 <= self.v_head_dim <= 256):
+            raise ValueError(f"attention: head sizes lie in 1 .. 256, got {self.head_dim} and {self.v_head_dim}")
+        self.q_width, self.k_width = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim
+        self.v_width, self.o_width = self.n_kv_heads * self.v_head_dim, self.n_heads * self.v_head_dim
+        stacked = [weights["w_q"], weights["w_k"], weights["w_v"]]
+        self.gated = weights.get("w_gate") is not None
+        if self.gated:
+            stacked.append(weights["w_gate"])
+        want = [self.q_width, self.k_width, self.v_width] + ([self.o_width] if self.gated else [])
+        if [w.shape[0] for w in stacked] != want or weights["w_out"].shape[1] != self.o_width:
+            raise ValueError(f"attention: projections of {[tuple(w.shape) for w in stacked]} and an output of "
+                             f"{tuple(weights['w_out'].shape)} do not fit {self.n_heads} heads, {self.n_kv_heads} kv heads "
+                             f"of {self.head_dim} (values {self.v_head_dim})")
+        self.w_in = matrix(torch.cat(stacked, dim=0), rt)
+        self.w_out = matrix(weights["w_out"], rt)
+        self.q_norm, self.k_norm = vector(weights["q_norm"], rt), vector(weights["k_norm"], rt)
+
+    def matrices(self):
+        return [self.w_in, self.w_out]
+
+    @property
+    def cache_spec(self) -> MemberSpec:
+        return MemberSpec(self.n_kv_heads, self.head_dim, self.window, self.v_head_dim, self.keep_first)
+
+    state_spec = None
+    capturable = True
+
+    def forward(self, h, residual, ctx, cache, state=None, writes_cache: bool = True):
+        proj = ops.linear(h, self.w_in, None, w_is_nk=True)
+        ops.head_norm(proj, self.n_heads, self.n_kv_heads, self.head_dim, self.q_norm, self.k_norm, self.norm_eps,
+                      self.norm_unit_offset)
+        at = self.q_width
+        q, k = proj[:, :at], proj[:, at: at + self.k_width]
+        at += self.k_width
+        v = proj[:, at: at + self.v_width]
+        gate = proj[:, at + self.v_width:] if self.gated else None
+        if writes_cache:
+            ops.kv_write(k, v, cache.k, cache.v, ctx.slot_mapping[cache.group], self.n_kv_heads, self.head_dim,
+                         cache.page_size, cache.page_stride, cache.n_pages, v_head_dim=self.v_head_dim)
+        mixed = ops.paged_attention(
+            q, cache.k, cache.v, cache.page_stride, cache.page_size, cache.n_pages, ctx.block_tables[cache.group],
+            ctx.row_entry, ctx.positions, ctx.seq_lens, self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
+            self.window, decode_only=ctx.decode_only, max_context=ctx.max_context, q_start=ctx.q_start,
+            n_tiles=ctx.n_attention_tiles, v_head_dim=self.v_head_dim, keep_first=self.keep_first, sink=self.sink, gate=gate)
+        return ops.linear(mixed, self.w_out, None, w_is_nk=True, residual=residual)

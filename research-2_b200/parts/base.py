@@ -66,11 +66,11 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    block: str  # arrangement, e.g. "pre_norm"
+    block: str  # arrangement, e.g. "pre_norm" or "parallel"
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: PartSpec | None  # None: a layer without a feed-forward (arrangements that allow it)
     norm_1: PartSpec
-    norm_2: PartSpec
+    norm_2: PartSpec | None = None  # None: an arrangement with one norm
 
 
 _REGISTRIES: dict[str, dict[str, Callable[..., Any]]] = {

@@ -39,3 +39,23 @@ class PreNormBlock:
         if getattr(consumer, "takes_lazy_norm", False) and getattr(norm, "can_be_lazy", False):
             return norm.forward(x, self.compute_dtype, lazy=True)
         return norm.forward(x, self.compute_dtype)
+
+
+@register_block("parallel")
+class ParallelBlock:
+    """x + mixer(h) + feed_forward(h) with h = norm_1(x): one norm, and both sublayers read its output. Each
+    sublayer's last matrix product adds its result to the float32 stream that it is handed, the mixer's to x
+    and the feed-forward's to that sum. A layer may have no feed-forward (None); there is no second norm."""
+
+    def __init__(self, norm_1, mixer, norm_2, feed_forward, compute_dtype):
+        if norm_2 is not None:
+            raise ValueError("a parallel block has one norm")
+        self.norm_1, self.mixer, self.norm_2, self.feed_forward = norm_1, mixer, None, feed_forward
+        self.compute_dtype = compute_dtype
+
+    def forward(self, x, ctx, cache=None, state=None, writes_cache: bool = True):
+        h = self.norm_1.forward(x, self.compute_dtype)
+        x = self.mixer.forward(h, x, ctx, cache, state, writes_cache)
+        if self.feed_forward is not None:
+            x = self.feed_forward.forward(h, x, ctx)
+        return x

@@ -1,7 +1,7 @@
 """Token embedding and the output head.
 
-The embedding gathers table rows into the float32 residual stream, adding the rows of an
-additive position table in the same kernel. The head normalises only the rows whose logits
+The embedding gathers table rows into the float32 residual stream, times a constant scale where a
+model has one, adding the rows of an additive position table in the same kernel. The head normalises only the rows whose logits
 are wanted and multiplies them with the [V, D] table (`x @ table^T`); GPT-2 ties the two
 tables (kelpie-models/kelpie_models/models/torch/gpt2.py:70,98-101).
 """
@@ -16,11 +16,12 @@ from .util import matrix
 
 
 class TokenEmbedding:
-    def __init__(self, table: torch.Tensor, rt: Runtime):
+    def __init__(self, table: torch.Tensor, rt: Runtime, scale: float = 1.0):
         self.table = matrix(table, rt)
+        self.scale = float(scale)  # table rows are multiplied by it on their way into the stream
 
     def forward(self, ctx, additive_table=None):
-        return ops.embed(ctx.input_ids, self.table, ctx.positions, additive_table)
+        return ops.embed(ctx.input_ids, self.table, ctx.positions, additive_table, scale=self.scale)
 
 
 class Head:

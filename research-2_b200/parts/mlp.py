@@ -1,7 +1,10 @@
-"""The dense feed-forward: act(h @ w_in + b_in) @ w_out + b_out, added to the residual stream.
-Reference: kelpie-models/kelpie_models/models/torch/gpt2.py:94-96."""
+"""Dense feed-forwards, added to the residual stream: act(h @ w_in + b_in) @ w_out + b_out
+(reference: kelpie-models/kelpie_models/models/torch/gpt2.py:94-96), and the gated form with clamped
+projections."""
 
 from __future__ import annotations
+
+import torch
 
 from ..kernels import ops
 from .base import Runtime, register_feed_forward
@@ -36,3 +39,28 @@ class DenseMLP:
 
     def forward(self, h, residual, ctx):
         return ops.mlp(h, self.w_in, self.b_in, self.activation, self.w_out, self.b_out, residual=residual)
+
+
+@register_feed_forward("gated_clamped")
+class GatedClampedMLP:
+    """W_down y with y = g * sigmoid(alpha * g) * (u + up_offset), g = min(W_gate h, limit) and
+    u = clamp(W_up h, -limit, limit). params: limit, alpha, up_offset. weights: w_gate [F, D], w_up [F, D],
+    w_down [D, F], all stored [out, in], no biases. The two input projections run as one product over the
+    stacked matrix [2 F, D]."""
+
+    def __init__(self, params: dict, weights: dict, rt: Runtime):
+        self.limit, self.alpha, self.up_offset = float(params["limit"]), float(params["alpha"]), float(params["up_offset"])
+        gate, up, down = weights["w_gate"], weights["w_up"], weights["w_down"]
+        if gate.shape != up.shape or down.shape != (gate.shape[1], gate.shape[0]):
+            raise ValueError(f"gated feed-forward: w_gate {tuple(gate.shape)}, w_up {tuple(up.shape)} and w_down {tuple(down.shape)} do not fit")
+        self.inner = gate.shape[0]
+        self.w_gate_up = matrix(torch.cat([gate, up], dim=0), rt)
+        self.w_down = matrix(down, rt)
+
+    def matrices(self):
+        return [self.w_gate_up, self.w_down]
+
+    def forward(self, h, residual, ctx):
+        gate_up = ops.linear(h, self.w_gate_up, None, w_is_nk=True)
+        y = ops.gated_act(gate_up, self.limit, self.alpha, self.up_offset)
+        return ops.linear(y, self.w_down, None, w_is_nk=True, residual=residual)

@@ -1,5 +1,5 @@
-"""LayerNorm with statistics in float32.
-Reference: kelpie-models/kelpie_models/kernels/ops/layer_norm.py:21-23."""
+"""Norms of rows with statistics in float32: LayerNorm
+(reference: kelpie-models/kelpie_models/kernels/ops/layer_norm.py:21-23) and RMS norm."""
 
 from __future__ import annotations
 
@@ -29,3 +29,19 @@ class LayerNorm:
         if lazy:
             return ops.NormedRows(x, self.gamma, self.beta, self.eps, out_dtype, rows=rows)
         return ops.layer_norm(x, self.gamma, self.beta, self.eps, out_dtype, rows=rows)
+
+
+@register_norm("rms_norm")
+class RMSNorm:
+    """x / sqrt(mean(x^2) + eps) * gain. params: eps; unit_offset (the stored weight lies around zero and the
+    gain is 1 + weight; default false: the weight is the gain). weights: weight."""
+
+    can_be_lazy = False
+
+    def __init__(self, params: dict, weights: dict, rt: Runtime):
+        self.eps = float(params["eps"])
+        self.unit_offset = bool(params.get("unit_offset", False))
+        self.weight = vector(weights["weight"], rt)
+
+    def forward(self, x, out_dtype, rows=None, lazy: bool = False):
+        return ops.rms_norm(x, self.weight, self.eps, out_dtype, rows=rows, unit_offset=self.unit_offset)
