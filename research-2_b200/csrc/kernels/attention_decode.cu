@@ -39,6 +39,11 @@ struct DecodeParams {
   const int32_t* row_entry; const int32_t* positions; const int32_t* seq_lens;
   int n_heads, n_kv_heads;
   float scale; int window;
+  // With a window, the entry's first `keep_first` keys stay visible beside the window's. `sink` adds one
+  // to every softmax's denominator (a key of score 0 that has no value). `gate` (may be null;
+  // [rows, n_heads * HD]) multiplies the output by its sigmoid. `split_p` carries the softmax's weights
+  // into the second product as the sum of two bfloat16 numbers instead of one rounded one.
+  int keep_first; int sink; const bf16* gate; int gate_row_stride; int split_p;
   int n_slices;
   float* part_o;   // [rows, n_heads, n_slices, HD]
   float* part_ml;  // [rows, n_heads, n_slices, 2]
@@ -68,6 +73,19 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
+}
+// (lo, hi) minus what `packed` holds of them, as a bfloat16 pair: x = bf16(x) + bf16(x - bf16(x)) to 16 bits
+__device__ __forceinline__ uint32_t pack_rest(float lo, float hi, uint32_t packed) {
+  const float2 head = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&packed));
+  return pack_bf16(lo - head.x, hi - head.y);
+}
+// The end of a row's softmax: with a sink the denominator counts one more key of score 0; with a gate the
+// output is multiplied by the sigmoid of the gate's value.
+__device__ __forceinline__ float finish(float o, float l, float mx, int sink, const bf16* gate) {
+  if (sink) l += mx > -INFINITY ? __expf(-mx) : 1.f;
+  float y = l > 0.f ? o / l : 0.f;
+  if (gate != nullptr) y *= 1.f / (1.f + __expf(-__bfloat162float(*gate)));
+  return y;
 }
 
 constexpr bool MMA_FITS = HD <= 128;   // the tensor-core form keeps HD / 2 output floats per lane
@@ -100,7 +118,12 @@ decode_kernel(const DecodeParams p) {
   const int seq_len = p.seq_lens[e];
   const int last = pos < seq_len - 1 ? pos : seq_len - 1;
   const int first = p.window > 0 ? (pos - p.window + 1 > 0 ? pos - p.window + 1 : 0) : 0;
-  const int n_keys = last - first + 1;
+  // The keys that the row sees are walked by a running index v: first the kept first keys (those below
+  // the window's start), then the window's. Key v of the walk lies at position v, or first + (v - kept).
+  const int kept = p.window > 0 ? min(p.keep_first, first) : 0;
+  const int n_keys = kept + last - first + 1;
+  const int v_of_pos = kept + pos - first;   // where the newest key stands in the walk
+  auto key_at = [&](int v) { return v < kept ? v : first + (v - kept); };
   // this slice's keys: equal runs of whole 32-key tiles
   const int tiles = (n_keys + 31) / 32;
   const int tiles_per = (tiles + p.n_slices - 1) / p.n_slices;
@@ -131,14 +154,15 @@ decode_kernel(const DecodeParams p) {
   // key's row comes from the projection's output (k_new, v_new), not from the cache.
   extern __shared__ __align__(16) uint8_t tile_smem[];
   uint8_t* my_smem = tile_smem + size_t(warp) * NBUF * 2 * 32 * ROW_BYTES;
-  const int tile_of_new = (p.k_new != nullptr && pos == last) ? (pos - first) / 32 : -1;
+  const int tile_of_new = (p.k_new != nullptr && pos == last) ? v_of_pos / 32 : -1;
 
   // lane r finds row r's place: element offsets from k_cache / v_cache; -1 for a row past the last key
   auto lookup = [&](int tile, long long& my_k, long long& my_v) {
-    const int j = first + tile * 32 + lane;
-    if (j > last) {
+    const int v = tile * 32 + lane;
+    const int j = key_at(v);
+    if (v >= n_keys) {
       my_k = my_v = -1;
-    } else if (tile == tile_of_new && j == pos) {
+    } else if (tile == tile_of_new && v == v_of_pos) {
       my_k = (p.k_new + size_t(t) * p.new_row_stride + size_t(kvh) * HD) - p.k_cache;
       my_v = (p.v_new + size_t(t) * p.new_row_stride + size_t(kvh) * HD) - p.v_cache;
     } else {
@@ -150,7 +174,7 @@ decode_kernel(const DecodeParams p) {
   // then consecutive lanes copy consecutive 16-byte pieces of a row, then the next row: whole
   // lines per request
   auto copy = [&](int tile, int buf, long long my_k, long long my_v) {
-    const int j0 = first + tile * 32;
+    const int v0 = tile * 32;
     const uint32_t kd = smem_u32(my_smem + (size_t(buf) * 2 + 0) * 32 * ROW_BYTES);
     const uint32_t vd = smem_u32(my_smem + (size_t(buf) * 2 + 1) * 32 * ROW_BYTES);
 #pragma unroll
@@ -159,7 +183,7 @@ decode_kernel(const DecodeParams p) {
       const int row = f / VECS, c = f % VECS;
       const long long ko = __shfl_sync(0xffffffffu, my_k, row);
       const long long vo = __shfl_sync(0xffffffffu, my_v, row);
-      const bool valid = ko >= 0 || (tile == tile_of_new && j0 + row == pos);
+      const bool valid = ko >= 0 || (tile == tile_of_new && v0 + row == v_of_pos);
       const int bytes = valid ? 16 : 0;  // 0 source bytes: zeros
       const bf16* ksrc = valid ? p.k_cache + ko + c * 8 : p.k_cache;
       const bf16* vsrc = valid ? p.v_cache + vo + c * 8 : p.v_cache;
@@ -200,7 +224,7 @@ decode_kernel(const DecodeParams p) {
   }
   int it = 0;
   for (int tile = tile_begin + warp; tile < tile_end; tile += WARPS, ++it) {
-    const int j0 = first + tile * 32;
+    const int v0 = tile * 32;
     const int buf = NBUF == 2 ? (it & 1) : 0;
     if (tile == tile_of_new) {
       // the newest key lies in this tile: this warp also puts its key and value into the cache
@@ -253,7 +277,7 @@ decode_kernel(const DecodeParams p) {
       for (int nt = 0; nt < 4; ++nt) {
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-          const bool seen = j0 + nt * 8 + 2 * tq + c <= last;
+          const bool seen = v0 + nt * 8 + 2 * tq + c < n_keys;
           sc[nt][c] = seen ? sc[nt][c] * p.scale : -INFINITY;
           sc[nt][2 + c] = seen ? sc[nt][2 + c] * p.scale : -INFINITY;
           mx_a = fmaxf(mx_a, sc[nt][c]);
@@ -297,6 +321,12 @@ decode_kernel(const DecodeParams p) {
       for (int kk = 0; kk < 2; ++kk) {
         const uint32_t a0 = pack_bf16(sc[2 * kk][0], sc[2 * kk][1]), a1 = pack_bf16(sc[2 * kk][2], sc[2 * kk][3]);
         const uint32_t a2 = pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]), a3 = pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+        // what the rounding to bfloat16 left of each weight, as a second bfloat16 operand
+        uint32_t r0 = 0, r1 = 0, r2 = 0, r3 = 0;
+        if (p.split_p) {
+          r0 = pack_rest(sc[2 * kk][0], sc[2 * kk][1], a0); r1 = pack_rest(sc[2 * kk][2], sc[2 * kk][3], a1);
+          r2 = pack_rest(sc[2 * kk + 1][0], sc[2 * kk + 1][1], a2); r3 = pack_rest(sc[2 * kk + 1][2], sc[2 * kk + 1][3], a3);
+        }
 #pragma unroll
         for (int dp = 0; dp < DT / 2; ++dp) {  // two 8-wide output tiles per ldmatrix
           uint32_t b0, b1, b2, b3;
@@ -304,6 +334,10 @@ decode_kernel(const DecodeParams p) {
           ldmatrix_x4_trans(vt + uint32_t(key * ROW_BYTES + (dp * 2 + (lane >> 4)) * 16), b0, b1, b2, b3);
           mma_bf16(o[2 * dp], a0, a1, a2, a3, b0, b1);
           mma_bf16(o[2 * dp + 1], a0, a1, a2, a3, b2, b3);
+          if (p.split_p) {
+            mma_bf16(o[2 * dp], r0, r1, r2, r3, b0, b1);
+            mma_bf16(o[2 * dp + 1], r0, r1, r2, r3, b2, b3);
+          }
         }
       }
       if (NBUF == 1) {
@@ -314,8 +348,7 @@ decode_kernel(const DecodeParams p) {
       }
       continue;
     }
-    const int j = j0 + lane;
-    const bool valid = j <= last;
+    const bool valid = v0 + lane < n_keys;
     float s[G];
 #pragma unroll
     for (int g = 0; g < G; ++g) s[g] = 0.f;
@@ -429,7 +462,8 @@ decode_kernel(const DecodeParams p) {
       }
     }
     if (p.n_slices == 1) {
-      p.out[size_t(t) * p.out_row_stride + size_t(h0 + g) * HD + d] = __float2bfloat16_rn(lsum > 0.f ? o / lsum : 0.f);
+      const bf16* gate = p.gate != nullptr ? p.gate + size_t(t) * p.gate_row_stride + size_t(h0 + g) * HD + d : nullptr;
+      p.out[size_t(t) * p.out_row_stride + size_t(h0 + g) * HD + d] = __float2bfloat16_rn(finish(o, lsum, mx, p.sink, gate));
     } else {
       size_t at = (size_t(t) * p.n_heads + h0 + g) * p.n_slices + slice;
       p.part_o[at * HD + d] = o;
@@ -465,7 +499,8 @@ decode_kernel(const DecodeParams p) {
             lsum += c * __ldcg(&p.part_ml[(base + s) * 2 + 1]);
           }
         }
-        p.out[size_t(t) * p.out_row_stride + size_t(h0 + g) * HD + d] = __float2bfloat16_rn(lsum > 0.f ? o / lsum : 0.f);
+        const bf16* gate = p.gate != nullptr ? p.gate + size_t(t) * p.gate_row_stride + size_t(h0 + g) * HD + d : nullptr;
+        p.out[size_t(t) * p.out_row_stride + size_t(h0 + g) * HD + d] = __float2bfloat16_rn(finish(o, lsum, mx, p.sink, gate));
       }
     }
   }
@@ -473,7 +508,8 @@ decode_kernel(const DecodeParams p) {
 
 // out[t, h, :] = sum_s exp(m_s - m) o_s / sum_s exp(m_s - m) l_s, slices in order.
 __global__ void merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out,
-                             int out_row_stride, int n_heads, int n_slices) {
+                             int out_row_stride, int n_heads, int n_slices, int sink, const bf16* __restrict__ gate,
+                             int gate_row_stride) {
   pdl_launch_dependents();  // the next kernel may begin its prologue
   pdl_wait();               // the previous kernel's writes are visible from here on
   const int t = blockIdx.y, h = blockIdx.x;
@@ -489,7 +525,8 @@ __global__ void merge_kernel(const float* __restrict__ part_o, const float* __re
         l += c * part_ml[(base + s) * 2 + 1];
       }
     }
-    out[size_t(t) * out_row_stride + size_t(h) * HD + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+    const bf16* gp = gate != nullptr ? gate + size_t(t) * gate_row_stride + size_t(h) * HD + d : nullptr;
+    out[size_t(t) * out_row_stride + size_t(h) * HD + d] = __float2bfloat16_rn(finish(o, l, mx, sink, gp));
   }
 }
 
@@ -554,6 +591,7 @@ extern "C" int r2_attention_decode(const void* q, int q_row_stride, void* out, i
   p.row_entry = row_entry; p.positions = positions; p.seq_lens = seq_lens;
   p.n_heads = n_heads; p.n_kv_heads = n_kv_heads;
   p.scale = scale; p.window = window; p.n_slices = n_slices;
+  p.keep_first = 0; p.sink = 0; p.gate = nullptr; p.gate_row_stride = 0; p.split_p = 0;
   p.part_o = scratch;
   p.part_ml = scratch != nullptr ? scratch + (long long)n_rows * n_heads * n_slices * HD : nullptr;
   p.k_new = nullptr; p.v_new = nullptr; p.new_row_stride = 0; p.slot_mapping = nullptr;
@@ -567,7 +605,8 @@ extern "C" int r2_attention_decode(const void* q, int q_row_stride, void* out, i
     default: return R2_UNSUPPORTED;
   }
   if (status != R2_OK || n_slices == 1) return status;
-  r2_launch(merge_kernel, dim3(dim3(n_heads, n_rows)), dim3(HD >= 128 ? 128 : 64), size_t(0), stream, p.part_o, p.part_ml, (bf16*)out, out_row_stride, n_heads, n_slices);
+  r2_launch(merge_kernel, dim3(dim3(n_heads, n_rows)), dim3(HD >= 128 ? 128 : 64), size_t(0), stream, p.part_o, p.part_ml, (bf16*)out, out_row_stride, n_heads, n_slices, p.sink,
+            p.gate, p.gate_row_stride);
   return launch_status();
 }
 
@@ -583,7 +622,7 @@ int launch_fused(const DecodeParams& p, int n_rows, cudaStream_t stream) { retur
 // the kernel itself, and the slices of a (row, kv head) are merged by whichever of their CTAs
 // finishes last, so there is neither a separate cache-write kernel nor a merge kernel.
 // `scratch` as for r2_attention_decode; `counters` holds n_rows * n_kv_heads ints that are
-// zero before the call and zero again after it.
+// zero before the call and zero again after it. `keep_first`, `sink`, `gate` and `split_p`: see DecodeParams.
 extern "C" int r2_attention_decode_fused(const void* q, int q_row_stride, void* out, int out_row_stride, void* k_cache,
                                          void* v_cache, long long page_stride, int page_size, int n_pages,
                                          const int32_t* block_tables, int table_width, const int32_t* row_entry,
@@ -591,8 +630,10 @@ extern "C" int r2_attention_decode_fused(const void* q, int q_row_stride, void* 
                                          int n_kv_heads, float scale, int window, int n_slices, const void* k_new,
                                          const void* v_new, int new_row_stride, const int32_t* slot_mapping,
                                          float* scratch, long long scratch_floats, int* counters, int n_counters,
+                                         int keep_first, int sink, const void* gate, int gate_row_stride, int split_p,
                                          cudaStream_t stream) {
   if (n_rows <= 0) return R2_OK;
+  if (keep_first < 0) return R2_BAD_SHAPE;
   if (n_heads < 1 || n_kv_heads < 1 || n_heads % n_kv_heads != 0 || page_size < 1 || window < 0 || n_slices < 1) return R2_BAD_SHAPE;
   if (n_slices > 1 && (scratch == nullptr || counters == nullptr || n_counters < n_rows * n_kv_heads ||
                        scratch_floats < r2_attention_decode_scratch_floats(n_rows, n_heads, n_slices))) return R2_BAD_SHAPE;
@@ -608,6 +649,7 @@ extern "C" int r2_attention_decode_fused(const void* q, int q_row_stride, void* 
   p.row_entry = row_entry; p.positions = positions; p.seq_lens = seq_lens;
   p.n_heads = n_heads; p.n_kv_heads = n_kv_heads;
   p.scale = scale; p.window = window; p.n_slices = n_slices;
+  p.keep_first = keep_first; p.sink = sink; p.gate = (const bf16*)gate; p.gate_row_stride = gate_row_stride; p.split_p = split_p;
   p.part_o = scratch;
   p.part_ml = scratch != nullptr ? scratch + (long long)n_rows * n_heads * n_slices * HD : nullptr;
   p.k_new = (const bf16*)k_new; p.v_new = (const bf16*)v_new; p.new_row_stride = new_row_stride;

@@ -53,6 +53,11 @@ struct PrefillParams {
   const int32_t* q_start; const int32_t* seq_lens; int n_entries;
   int n_heads, n_kv_heads;
   float scale; int window;
+  // With a window, an entry's first `keep_first` keys stay visible beside the window's. `sink` adds one to
+  // every softmax's denominator (a key of score 0 that has no value). `gate` (may be null;
+  // [rows, n_heads * HD]) multiplies the output by its sigmoid. `split_p` carries the softmax's weights
+  // into the second product as the sum of two bfloat16 numbers instead of one rounded one.
+  int keep_first; int sink; const bf16* gate; int gate_row_stride; int split_p;
   int box_rows;      // TMA form: key rows per tensor copy (the page size, or 64 for larger pages)
   int* error_flag;   // TMA form: where a bounded wait that ran out is recorded
 };
@@ -73,6 +78,13 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_
 
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+
+// (lo, hi) minus what `packed` holds of them, as a bfloat16 pair: x = bf16(x) + bf16(x - bf16(x)) to 16 bits
+__device__ __forceinline__ uint32_t pack_rest(float lo, float hi, uint32_t packed) {
+  const float2 head = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&packed));
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo - head.x, hi - head.y);
+  return *reinterpret_cast<uint32_t*>(&v);
 }
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -136,6 +148,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
   const int rows_here = min(BM, n_rows - r0);
   const int pmin = start + r0, pmax = start + r0 + rows_here - 1;
   const int lo = p.window > 0 ? max(0, pmin - p.window + 1) : 0;
+  const int keep = p.window > 0 ? p.keep_first : 0;   // keys below it stay visible however far the window has moved
   const int32_t* table = p.block_tables + size_t(e) * p.table_width;
 
   // ---- the query tile ----
@@ -158,7 +171,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       int j = j0 + (tid + i * WARPS * 32) / CHUNKS;
       // the entry is checked where it is used, so that nothing waits for this load here; a row
       // outside the tile's keys is marked with a page below every valid one
-      pages[i] = (j >= lo && j <= pmax) ? table[page_index(j, p.page_size, p.page_shift)] : INT_MIN;
+      pages[i] = ((j >= lo || j < keep) && j <= pmax) ? table[page_index(j, p.page_size, p.page_shift)] : INT_MIN;
     }
   };
   auto load_tile = [&](int j0, int stage, const int (&pages)[PIECES]) {
@@ -176,8 +189,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     }
   };
 
+  // The key tiles of the walk: first those that hold kept first keys below the window's tiles, then the
+  // window's. Tile `it` starts at key tile_j0(it).
   const int j_first = lo / BN * BN;
-  const int n_tiles = (pmax - j_first) / BN + 1;
+  const int n_kept_tiles = (min(keep, j_first) + BN - 1) / BN;
+  const int n_tiles = n_kept_tiles + (pmax - j_first) / BN + 1;
+  auto tile_j0 = [&](int it) { return it < n_kept_tiles ? it * BN : j_first + (it - n_kept_tiles) * BN; };
   int pages_next[PIECES];
 
   // TMA form: lane b of the producer warp brings box b of a tile (box_rows key rows of one page,
@@ -190,7 +207,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
     box_page = INT_MIN;
     if (lane < n_boxes) {
       const int jb = j0 + lane * p.box_rows;
-      if (jb + p.box_rows - 1 >= lo && jb <= pmax) box_page = table[page_index(jb, p.page_size, p.page_shift)];
+      if ((jb + p.box_rows - 1 >= lo || jb < keep) && jb <= pmax) box_page = table[page_index(jb, p.page_size, p.page_shift)];
     }
   };
   auto box_issue = [&](int j0, int stage) {  // the whole producer warp, converged
@@ -222,15 +239,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       // ---- the producer warp: tile after tile into the ring, a stage as soon as the computing
       // warps have let go of it (the ring's first round finds every stage free) -----------------
       uint32_t round_parity = 0;
-      box_lookup(j_first);
+      box_lookup(tile_j0(0));
       for (int it = 0; it < n_tiles; ++it) {
         const int stage = it % STAGES;
         if (it >= STAGES && !mbar_wait(empty_base + uint32_t(stage) * 8u, round_parity ^ 1u)) {
           if (lane == 0) atomicMax(p.error_flag, R2_ERR_TIMEOUT_KV_TILE);
           break;
         }
-        box_issue(j_first + it * BN, stage);
-        if (it + 1 < n_tiles) box_lookup(j_first + (it + 1) * BN);
+        box_issue(tile_j0(it), stage);
+        if (it + 1 < n_tiles) box_lookup(tile_j0(it + 1));
         if (stage == STAGES - 1) round_parity ^= 1u;
       }
       return;
@@ -240,12 +257,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
 #pragma unroll
     for (int t = 0; t < STAGES - 1; ++t) {
       if (t < n_tiles) {
-        pages_of(j_first + t * BN, pages_next);
-        load_tile(j_first + t * BN, t, pages_next);
+        pages_of(tile_j0(t), pages_next);
+        load_tile(tile_j0(t), t, pages_next);
       }
       asm volatile("cp.async.commit_group;" ::: "memory");
     }
-    if (STAGES - 1 < n_tiles) pages_of(j_first + (STAGES - 1) * BN, pages_next);
+    if (STAGES - 1 < n_tiles) pages_of(tile_j0(STAGES - 1), pages_next);
   }
   uint32_t tile_parity = 0;  // TMA form: parity of the ring's current round
   bool tiles_ok = true;
@@ -261,7 +278,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
 
   for (int it = 0; it < n_tiles; ++it) {
     const int stage = it % STAGES;
-    const int j0 = j_first + it * BN;
+    const int j0 = tile_j0(it);
     if (TMA) {
       if (it == 0) {
         asm volatile("cp.async.wait_group 0;" ::: "memory");  // the query tile
@@ -273,13 +290,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         tiles_ok = false;
       }
       if (stage == STAGES - 1) tile_parity ^= 1u;
-      if (j0 < lo || j0 + BN - 1 > pmax) {
+      if ((j0 < lo && j0 + BN > keep) || j0 + BN - 1 > pmax) {
         // Rows of the tile outside the keys that any query row may see were not copied, or hold
         // whatever their slots held: their scores are masked by selection, but a value row is
         // multiplied by p = 0, so it has to be finite. They are set to zero.
         for (int row = tid; row < BN; row += WARPS * 32) {
           const int j = j0 + row;
-          if (j < lo || j > pmax) {
+          if ((j < lo && j >= keep) || j > pmax) {
             const uint32_t dst = smem_u32(v_s) + uint32_t(stage * TMA_TILE_BYTES + row * 128);
 #pragma unroll
             for (int c = 0; c < 8; ++c) asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst + c * 16), "r"(0u) : "memory");
@@ -293,9 +310,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       // barrier every thread's part of it is visible and the stage of tile it - 1 is free
       asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
       __syncthreads();
-      if (it + STAGES - 1 < n_tiles) load_tile(j0 + (STAGES - 1) * BN, (it + STAGES - 1) % STAGES, pages_next);
+      if (it + STAGES - 1 < n_tiles) load_tile(tile_j0(it + STAGES - 1), (it + STAGES - 1) % STAGES, pages_next);
       asm volatile("cp.async.commit_group;" ::: "memory");
-      if (it + STAGES < n_tiles) pages_of(j0 + STAGES * BN, pages_next);
+      if (it + STAGES < n_tiles) pages_of(tile_j0(it + STAGES), pages_next);
     }
     if (it == 0) {
 #pragma unroll
@@ -334,7 +351,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       // every key of this tile is visible to every row of this warp: no mask to evaluate
       const int warp_pmin = pmin + warp * 16, warp_pmax = pmin + min(warp * 16 + 15, rows_here - 1);
       const bool all_visible = j0 + BN - 1 <= warp_pmin && warp * 16 + 15 < rows_here &&
-                               (p.window == 0 || j0 > warp_pmax - p.window);
+                               (p.window == 0 || j0 > warp_pmax - p.window || j0 + BN <= keep);
       // (the scale is positive, so the largest raw score is the largest scaled one; it goes into
       // the exponent's multiply-add)
       if (all_visible) {
@@ -351,13 +368,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
         // written with && and || over the position compiles to a chain of branches per element)
         const int hi_a = row_a < rows_here ? pos_a - j0 : -1, hi_b = row_b < rows_here ? pos_b - j0 : -1;
         const int lo_a = p.window > 0 ? pos_a - p.window + 1 - j0 : 0, lo_b = p.window > 0 ? pos_b - p.window + 1 - j0 : 0;
+        const int kf = keep - j0;   // keys of the tile below it are kept first keys
 #pragma unroll
         for (int nt = 0; nt < BN / 8; ++nt) {
 #pragma unroll
           for (int c = 0; c < 2; ++c) {
             const int k = nt * 8 + 2 * tq + c;
-            const bool va = (k <= hi_a) & (k >= lo_a);
-            const bool vb = (k <= hi_b) & (k >= lo_b);
+            const bool va = (k <= hi_a) & ((k >= lo_a) | (k < kf));
+            const bool vb = (k <= hi_b) & ((k >= lo_b) | (k < kf));
             s[nt][c] = va ? s[nt][c] : -INFINITY;
             s[nt][2 + c] = vb ? s[nt][2 + c] : -INFINITY;
             mx_a = fmaxf(mx_a, s[nt][c]);
@@ -404,6 +422,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       for (int kk = 0; kk < BN / 16; ++kk) {
         uint32_t a0 = pack_bf16(s[2 * kk][0], s[2 * kk][1]), a1 = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
         uint32_t a2 = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]), a3 = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+        // what the rounding to bfloat16 left of each weight, as a second bfloat16 operand
+        uint32_t r0 = 0, r1 = 0, r2 = 0, r3 = 0;
+        if (p.split_p) {
+          r0 = pack_rest(s[2 * kk][0], s[2 * kk][1], a0); r1 = pack_rest(s[2 * kk][2], s[2 * kk][3], a1);
+          r2 = pack_rest(s[2 * kk + 1][0], s[2 * kk + 1][1], a2); r3 = pack_rest(s[2 * kk + 1][2], s[2 * kk + 1][3], a3);
+        }
 #pragma unroll
         for (int dp = 0; dp < DTILES / 2; ++dp) {  // two 8-wide output tiles per ldmatrix
           uint32_t b0, b1, b2, b3;
@@ -411,6 +435,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
           ldmatrix_x4_trans(piece(vt, key, dp * 2 + (lane >> 4)), b0, b1, b2, b3);
           mma_bf16(o[2 * dp], a0, a1, a2, a3, b0, b1);
           mma_bf16(o[2 * dp + 1], a0, a1, a2, a3, b2, b3);
+          if (p.split_p) {
+            mma_bf16(o[2 * dp], r0, r1, r2, r3, b0, b1);
+            mma_bf16(o[2 * dp + 1], r0, r1, r2, r3, b2, b3);
+          }
         }
       }
     }
@@ -422,17 +450,31 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
 
+  if (p.sink) {  // one more key of score 0 in every denominator (running maxima are in units of log2 e)
+    l_run[0] += m_run[0] > -INFINITY ? fast_exp2(-m_run[0]) : 1.f;
+    l_run[1] += m_run[1] > -INFINITY ? fast_exp2(-m_run[1]) : 1.f;
+  }
   const float inv_a = l_run[0] > 0.f ? 1.f / l_run[0] : 0.f, inv_b = l_run[1] > 0.f ? 1.f / l_run[1] : 0.f;
 #pragma unroll
   for (int dt = 0; dt < DTILES; ++dt) {
     int d = dt * 8 + 2 * tq;
     if (row_a < rows_here) {
-      __nv_bfloat162 v = __floats2bfloat162_rn(o[dt][0] * inv_a, o[dt][1] * inv_a);
-      *reinterpret_cast<__nv_bfloat162*>(p.out + size_t(t0 + r0 + row_a) * p.out_row_stride + size_t(h) * HD + d) = v;
+      float y0 = o[dt][0] * inv_a, y1 = o[dt][1] * inv_a;
+      if (p.gate != nullptr) {
+        const float2 gv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p.gate + size_t(t0 + r0 + row_a) * p.gate_row_stride + size_t(h) * HD + d));
+        y0 *= 1.f / (1.f + __expf(-gv.x));
+        y1 *= 1.f / (1.f + __expf(-gv.y));
+      }
+      *reinterpret_cast<__nv_bfloat162*>(p.out + size_t(t0 + r0 + row_a) * p.out_row_stride + size_t(h) * HD + d) = __floats2bfloat162_rn(y0, y1);
     }
     if (row_b < rows_here) {
-      __nv_bfloat162 v = __floats2bfloat162_rn(o[dt][2] * inv_b, o[dt][3] * inv_b);
-      *reinterpret_cast<__nv_bfloat162*>(p.out + size_t(t0 + r0 + row_b) * p.out_row_stride + size_t(h) * HD + d) = v;
+      float y0 = o[dt][2] * inv_b, y1 = o[dt][3] * inv_b;
+      if (p.gate != nullptr) {
+        const float2 gv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p.gate + size_t(t0 + r0 + row_b) * p.gate_row_stride + size_t(h) * HD + d));
+        y0 *= 1.f / (1.f + __expf(-gv.x));
+        y1 *= 1.f / (1.f + __expf(-gv.y));
+      }
+      *reinterpret_cast<__nv_bfloat162*>(p.out + size_t(t0 + r0 + row_b) * p.out_row_stride + size_t(h) * HD + d) = __floats2bfloat162_rn(y0, y1);
     }
   }
 }
@@ -463,14 +505,17 @@ int launch(const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p,
 
 // n_tiles: the sum over entries of ceil(rows / 64), which the host knows from the batch (more is
 // harmless: the CTAs beyond find no tile). error_flag: a device word in which a bounded wait that
-// ran out is recorded (may be null; the tensor-copy form is then not used).
+// ran out is recorded (may be null; the tensor-copy form is then not used). `keep_first`, `sink`, `gate`
+// and `split_p`: see PrefillParams.
 extern "C" int r2_attention_prefill(const void* q, int q_row_stride, void* out, int out_row_stride, const void* k_cache,
                                     const void* v_cache, long long page_stride, int page_size, int n_pages,
                                     const int32_t* block_tables, int table_width, const int32_t* q_start,
                                     const int32_t* seq_lens, int n_entries, int n_tiles, int n_heads, int n_kv_heads,
-                                    float scale, int window, int* error_flag, cudaStream_t stream) {
+                                    float scale, int window, int* error_flag, int keep_first, int sink, const void* gate,
+                                    int gate_row_stride, int split_p, cudaStream_t stream) {
   if (n_entries <= 0 || n_tiles <= 0) return R2_OK;
-  if (n_heads < 1 || n_kv_heads < 1 || n_heads % n_kv_heads != 0 || page_size < 1 || window < 0) return R2_BAD_SHAPE;
+  if (n_heads < 1 || n_kv_heads < 1 || n_heads % n_kv_heads != 0 || page_size < 1 || window < 0 || keep_first < 0) return R2_BAD_SHAPE;
+  if (gate != nullptr && (gate_row_stride % 2 != 0 || (reinterpret_cast<uintptr_t>(gate) & 3))) return R2_BAD_ALIGN;
   if (page_stride % 8 != 0 || q_row_stride % 8 != 0 || out_row_stride % 2 != 0 || (reinterpret_cast<uintptr_t>(k_cache) & 15) ||
       (reinterpret_cast<uintptr_t>(v_cache) & 15) || (reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(out) & 3)) {
     return R2_BAD_ALIGN;
@@ -485,6 +530,7 @@ extern "C" int r2_attention_prefill(const void* q, int q_row_stride, void* out, 
   p.q_start = q_start; p.seq_lens = seq_lens; p.n_entries = n_entries;
   p.n_heads = n_heads; p.n_kv_heads = n_kv_heads;
   p.scale = scale; p.window = window;
+  p.keep_first = keep_first; p.sink = sink; p.gate = (const bf16*)gate; p.gate_row_stride = gate_row_stride; p.split_p = split_p;
   p.box_rows = 0;
   p.error_flag = error_flag;
   CUtensorMap mk, mv;

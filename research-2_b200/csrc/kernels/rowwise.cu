@@ -169,7 +169,7 @@ extern "C" int r2_layer_norm(const float* x, const int32_t* rows, const float* g
 // page * page_size + offset; inside a page the layout is [kv_head][offset][head_dim], and a
 // page of this layer starts every `page_stride` elements. Values may have a head size of their own.
 template <typename A, typename C>
-__global__ void kv_write_kernel(const A* __restrict__ k_src, const A* __restrict__ v_src, int src_row_stride,
+__global__ void kv_write_kernel(const A* __restrict__ k_src, const A* __restrict__ v_src, int src_row_stride, int v_row_stride,
                                 C* __restrict__ k_cache, C* __restrict__ v_cache,
                                 const int32_t* __restrict__ slot_mapping, int n_kv_heads, int head_dim, int v_head_dim,
                                 int page_size, long long page_stride, int n_pages) {
@@ -180,7 +180,7 @@ __global__ void kv_write_kernel(const A* __restrict__ k_src, const A* __restrict
   int page = slot / page_size, off = slot % page_size;
   if (slot < 0 || page >= n_pages) return;  // slots are validated on the host; never write outside the pool
   const A* ks = k_src + size_t(t) * src_row_stride;
-  const A* vs = v_src + size_t(t) * src_row_stride;
+  const A* vs = v_src + size_t(t) * v_row_stride;
   for (int i = threadIdx.x; i < n_kv_heads * head_dim; i += blockDim.x) {
     int h = i / head_dim, d = i % head_dim;
     k_cache[size_t(page) * page_stride + (size_t(h) * page_size + off) * head_dim + d] = from_float<C>(to_float(ks[i]));
@@ -191,7 +191,7 @@ __global__ void kv_write_kernel(const A* __restrict__ k_src, const A* __restrict
   }
 }
 
-extern "C" int r2_kv_write(const void* k_src, const void* v_src, int src_row_stride, void* k_cache, void* v_cache,
+extern "C" int r2_kv_write(const void* k_src, const void* v_src, int src_row_stride, int v_row_stride, void* k_cache, void* v_cache,
                            const int32_t* slot_mapping, int n_rows, int n_kv_heads, int head_dim, int v_head_dim, int page_size,
                            long long page_stride, int n_pages_total, int dtype, cudaStream_t stream) {
   if (n_rows <= 0) return R2_OK;
@@ -199,11 +199,11 @@ extern "C" int r2_kv_write(const void* k_src, const void* v_src, int src_row_str
   int width = n_kv_heads * (head_dim > v_head_dim ? head_dim : v_head_dim);
   int threads = width >= 256 ? 256 : 128;
   if (dtype == R2_F32) {
-    r2_launch(kv_write_kernel<float, float>, dim3(n_rows), dim3(threads), size_t(0), stream, (const float*)k_src, (const float*)v_src, src_row_stride,
+    r2_launch(kv_write_kernel<float, float>, dim3(n_rows), dim3(threads), size_t(0), stream, (const float*)k_src, (const float*)v_src, src_row_stride, v_row_stride,
                                                                   (float*)k_cache, (float*)v_cache, slot_mapping,
                                                                   n_kv_heads, head_dim, v_head_dim, page_size, page_stride, n_pages_total);
   } else if (dtype == R2_BF16) {
-    r2_launch(kv_write_kernel<bf16, bf16>, dim3(n_rows), dim3(threads), size_t(0), stream, (const bf16*)k_src, (const bf16*)v_src, src_row_stride,
+    r2_launch(kv_write_kernel<bf16, bf16>, dim3(n_rows), dim3(threads), size_t(0), stream, (const bf16*)k_src, (const bf16*)v_src, src_row_stride, v_row_stride,
                                                                 (bf16*)k_cache, (bf16*)v_cache, slot_mapping,
                                                                 n_kv_heads, head_dim, v_head_dim, page_size, page_stride, n_pages_total);
   } else {

@@ -28,10 +28,11 @@ class Replay:
     rounded up to a multiple of `round_to`; the pool gets the pages for that many (a request whose
     rounded count is no multiple of the page size may need one page more, so with such a page
     size the pool gets one extra page per live request). `capture` runs the steps as CUDA graphs
-    where the step function has one for the shape, as generation does."""
+    where the step function has one for the shape, as generation does. `max_seq_len` (0: the pool's
+    size, or the model's own limit if that is shorter) is the longest sequence that is admitted."""
 
     def __init__(self, model_dir: str, dtype: str, max_tokens: int, block_size: int = 16, device: str = "cuda:0",
-                 max_live: int = 4, round_to: int = 64, capture: bool = False):
+                 max_live: int = 4, round_to: int = 64, capture: bool = False, max_seq_len: int = 0):
         if max_tokens < 1:
             raise ValueError(f"--max-tokens must be >= 1, got {max_tokens}")
         if block_size < 1 or max_live < 1 or round_to < 1:
@@ -39,7 +40,8 @@ class Replay:
         self.model = load_model(model_dir, dtype=dtype, device=device)
         num_pages = -(-max_tokens // block_size) + (max_live if round_to % block_size else 0)
         # no request holds more than the pool: a model without a length limit of its own is run up to there
-        longest = min(self.model.max_seq_len, -(-max_tokens // round_to) * round_to)
+        # (`max_seq_len` says otherwise: a model whose layers all have windows can run sequences beyond its pool)
+        longest = min(self.model.max_seq_len, max_seq_len or -(-max_tokens // round_to) * round_to)
         self.step_fn = StepFunction(self.model, block_size, num_pages, max_live, capture=capture, capture_after=0,
                                     max_seq_len=longest)
         self.cache = CacheManager(self.step_fn.cache_groups(), max_live, self.step_fn.max_seq_len)

@@ -248,6 +248,22 @@ def use_tensor_core_gemm(on: bool) -> bool:
     return before
 
 
+_exact_weights = os.environ.get("R2_EXACT_WEIGHTS", "1") != "0"
+
+
+def use_exact_weights(on: bool) -> bool:
+    """Attention that has a sink, kept first keys or a gate computes its softmax weights in float32 and, in
+    the tensor-core kernels, hands them to the second product as the sum of two bfloat16 terms (16 bits of
+    mantissa) instead of one rounded term. Off: one term, as the plain attention does. Returns the previous setting."""
+    global _exact_weights
+    before, _exact_weights = _exact_weights, bool(on)
+    return before
+
+
+def exact_weights() -> bool:
+    return _exact_weights
+
+
 _kv_in_epilogue = os.environ.get("R2_KV_IN_EPILOGUE", "1") != "0"
 
 
@@ -612,10 +628,7 @@ def kv_write(k_src: torch.Tensor, v_src: torch.Tensor, k_cache: torch.Tensor, v_
     if (k_src.shape[1] != n_kv_heads * head_dim or v_src.shape[1] != n_kv_heads * v_head_dim or v_src.shape[0] != n
             or slot_mapping.shape[0] < n):
         raise KernelError("kv_write: shapes do not fit")
-    stride = _rows(k_src, "k_src")
-    if _rows(v_src, "v_src") != stride:
-        raise KernelError("kv_write: k and v must share a row stride")
-    status = _lib("rowwise").r2_kv_write(_p(k_src), _p(v_src), stride, _p(k_cache), _p(v_cache), _p(slot_mapping), n,
+    status = _lib("rowwise").r2_kv_write(_p(k_src), _p(v_src), _rows(k_src, "k_src"), _rows(v_src, "v_src"), _p(k_cache), _p(v_cache), _p(slot_mapping), n,
                                         n_kv_heads, head_dim, v_head_dim, page_size, C.c_longlong(page_stride), n_pages,
                                         dtype_code(k_src.dtype), _stream())
     _check(status, "kv_write")
@@ -656,9 +669,10 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
             raise KernelError(f"attention: gate {tuple(gate.shape)} is not [T, {n_heads} * {v_head_dim}]")
         gate_stride = _rows(gate, "gate")
     group = n_heads // max(n_kv_heads, 1)
-    # what only the general kernel takes: a value head size of its own, kept first keys, a sink, an output gate,
-    # or a head size that is no multiple of 16
-    plain = v_head_dim == head_dim and keep_first == 0 and not sink and gate is None and head_dim % 16 == 0
+    # only the general kernel takes a value head size of its own or a head size that is no multiple of 16; kept
+    # first keys, a sink and an output gate are taken by the mma.sync prefill kernel and the fused decode kernel
+    fits = v_head_dim == head_dim and head_dim % 16 == 0
+    plain = fits and keep_first == 0 and not sink and gate is None
     if plain and q.dtype == torch.bfloat16 and decode_only and _fast_attention and group in (1, 2, 4, 8):
         lib = _lib_for_head_dim("attention_decode", head_dim)
         n_slices = decode_slices(n, n_kv_heads, max_context, q.device)
@@ -689,15 +703,15 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
             _check(status, "paged_attention (prefill, tcgen05)")
             _used("attention_prefill_tc")
             return out
-    if (plain and q.dtype == torch.bfloat16 and _fast_attention and q_start is not None and n_tiles > 0 and head_dim <= 128
-            and _rows(q, "q") % 8 == 0 and q.data_ptr() % 16 == 0):
+    if (fits and q.dtype == torch.bfloat16 and _fast_attention and q_start is not None and n_tiles > 0 and head_dim <= 128
+            and _rows(q, "q") % 8 == 0 and q.data_ptr() % 16 == 0 and (gate is None or (gate_stride % 2 == 0 and gate.data_ptr() % 4 == 0))):
         _need(q_start, "q_start", torch.int32, 1)
         lib = _lib_for_head_dim("attention_prefill", head_dim)
         status = lib.r2_attention_prefill(
             _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(k_cache), _p(v_cache), C.c_longlong(page_stride),
             page_size, n_pages, _p(block_tables), block_tables.shape[1], _p(q_start), _p(seq_lens),
             q_start.shape[0] - 1, n_tiles, n_heads, n_kv_heads, C.c_float(scale), window, _p(_workspace(q.device).error),
-            _stream())
+            keep_first, int(bool(sink)), _p(gate), gate_stride, int(_exact_weights and not plain), _stream())
         _check(status, "paged_attention (prefill)")
         _used("attention_prefill")
         return out
@@ -715,11 +729,13 @@ def decode_attention_fused(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Te
                            k_cache: torch.Tensor, v_cache: torch.Tensor, page_stride: int, page_size: int, n_pages: int,
                            block_tables: torch.Tensor, row_entry: torch.Tensor, positions: torch.Tensor,
                            seq_lens: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
-                           window: int, max_context: int) -> torch.Tensor | None:
+                           window: int, max_context: int, keep_first: int = 0, sink: bool = False,
+                           gate: torch.Tensor | None = None, exact_weights: bool = False) -> torch.Tensor | None:
     """Decode attention in ONE launch for a batch in which every row is an entry of its own: the
     kernel writes the new keys and values to their cache slots, and the slice that finishes last
     merges all slices of its row. Returns None when it does not take the case (the caller then writes
-    the cache and calls `paged_attention`)."""
+    the cache and calls `paged_attention`). `keep_first`, `sink` and `gate` as in `paged_attention`;
+    `exact_weights` carries the softmax's weights into the second product as two bfloat16 terms."""
     group = n_heads // max(n_kv_heads, 1)
     if not (_fast_attention and _fused_decode and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
             and group in (1, 2, 4, 8) and head_dim % 16 == 0):
@@ -733,21 +749,31 @@ def decode_attention_fused(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Te
     stride = _rows(k_new, "k_new")
     if _rows(v_new, "v_new") != stride or k_new.shape != (n, n_kv_heads * head_dim) or slot_mapping.shape[0] < n:
         raise KernelError("decode attention: the new keys and values do not fit the rows")
+    if window > 0:
+        max_context = min(max_context, window + keep_first)   # what a row reads at most
     slices = decode_slices(n, n_kv_heads, max_context, q.device)
     lib = _lib_for_head_dim("attention_decode", head_dim)
     ws = _workspace(q.device)
     if (lib.r2_attention_decode_scratch_floats(n, n_heads, slices) > ws.floats.numel()
             or n * n_kv_heads > ws.counters.numel()):
         slices = 1
+    gate_stride = 0
+    if gate is not None:
+        _need(gate, "gate", torch.bfloat16, 2)
+        if gate.shape != (n, n_heads * head_dim):
+            raise KernelError(f"decode attention: gate {tuple(gate.shape)} is not [T, {n_heads} * {head_dim}]")
+        gate_stride = _rows(gate, "gate")
     out = torch.empty(n, n_heads * head_dim, dtype=q.dtype, device=q.device)
     status = lib.r2_attention_decode_fused(
         _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(k_cache), _p(v_cache), C.c_longlong(page_stride), page_size,
         n_pages, _p(block_tables), block_tables.shape[1], _p(row_entry), _p(positions), _p(seq_lens), n, n_heads,
         n_kv_heads, C.c_float(scale), window, slices, _p(k_new), _p(v_new), stride, _p(slot_mapping), _p(ws.floats),
-        C.c_longlong(ws.floats.numel()), _p(ws.counters), ws.counters.numel(), _stream())
+        C.c_longlong(ws.floats.numel()), _p(ws.counters), ws.counters.numel(), keep_first, int(bool(sink)), _p(gate),
+        gate_stride, int(bool(exact_weights)), _stream())
     if status == -4:
         return None
     _check(status, "decode attention (fused)")
+    _used("attention_decode_fused")
     return out
 
 

@@ -158,6 +158,15 @@ class QKNormAttention:
         at += self.k_width
         v = proj[:, at: at + self.v_width]
         gate = proj[:, at + self.v_width:] if self.gated else None
+        if writes_cache and ctx.decode_only and self.v_head_dim == self.head_dim:
+            # one new token per row: the kernel puts the new key and value into the cache itself
+            mixed = ops.decode_attention_fused(
+                q, k, v, ctx.slot_mapping[cache.group], cache.k, cache.v, cache.page_stride, cache.page_size,
+                cache.n_pages, ctx.block_tables[cache.group], ctx.row_entry, ctx.positions, ctx.seq_lens, self.n_heads,
+                self.n_kv_heads, self.head_dim, self.scale, self.window, ctx.max_context, keep_first=self.keep_first,
+                sink=self.sink, gate=gate, exact_weights=ops.exact_weights())
+            if mixed is not None:
+                return ops.linear(mixed, self.w_out, None, w_is_nk=True, residual=residual)
         if writes_cache:
             ops.kv_write(k, v, cache.k, cache.v, ctx.slot_mapping[cache.group], self.n_kv_heads, self.head_dim,
                          cache.page_size, cache.page_stride, cache.n_pages, v_head_dim=self.v_head_dim)
