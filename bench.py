@@ -19,6 +19,9 @@ A "step" is one decode step. The default run decodes a batch of 8 requests whose
              and 90th-percentile time to a request's first token
   kernels    the step's dominant kernels one by one: microseconds and fraction of the measured peak
 
+`--design zirunex` prints, instead, the same decode and prefill points for Zirunex models with the layer sizes
+of `--model` beside GPT-2's, and the design's kernels one by one beside their likes.
+
 `--model gpt2-355M` and `--model gpt2-1.5B` run the same at those sizes (the 1.5B decode workload has
 1,000-token prompts and 24 new tokens, which bounds its steps).
 
@@ -138,7 +141,7 @@ class DeviceLoopGraph:
         from research_2_b200.kernels import ops
 
         self.host = StepBatch(BatchLayout(batch, batch, batch, step_fn.table_widths), pinned=True)
-        self.host.max_context_bound = step_fn.model.max_seq_len
+        self.host.max_context_bound = step_fn.max_seq_len
         self.host.pad()
         self.host.set_logit_rows([])
         self.host.set_sampling([], [], [], [], [])
@@ -172,8 +175,8 @@ class DecodeLoop:
         self.torch, self.np = torch, np
         self.batch, self.n_steps = batch, n_steps
         pages = batch * (CONTEXT // PAGE)
-        self.step_fn = StepFunction(model, PAGE, pages, batch, capture=True)
-        self.cache = CacheManager(self.step_fn.cache_groups(), batch, model.max_seq_len)
+        self.step_fn = StepFunction(model, PAGE, pages, batch, capture=True, max_seq_len=min(model.max_seq_len, CONTEXT))
+        self.cache = CacheManager(self.step_fn.cache_groups(), batch, self.step_fn.max_seq_len)
         gen = torch.Generator().manual_seed(SEED + 100 + batch)
         self.prompts = torch.randint(0, model.vocab_size, (batch, PROMPT_LEN), generator=gen, dtype=torch.int32).numpy()
         total = PROMPT_LEN + n_steps
@@ -226,9 +229,13 @@ class DecodeLoop:
 
     def kv_bytes(self, first_step: int, n: int, model) -> float:
         """Average bytes of cache that one of the steps [first_step, first_step + n) reads."""
-        per_token = sum(2 * m.n_kv_heads * m.head_dim for m in model.cache_members) * self.step_fn.arena.tensors[0].element_size()
+        size = self.step_fn.arena.tensors[0].element_size()
         ctx = PROMPT_LEN + first_step + (n - 1) / 2.0
-        return self.batch * ctx * per_token
+        total = 0.0
+        for m in model.cache_members:   # a member with a window reads its window and its kept first tokens only
+            seen = min(ctx, m.window + m.keep_first) if m.window > 0 else ctx
+            total += m.n_kv_heads * (m.head_dim + m.value_dim) * size * seen
+        return self.batch * total
 
 
 def decode_point(model, batch: int, steps: int, warmup: int) -> tuple[float, float, "DecodeLoop", float]:
@@ -244,8 +251,9 @@ def prefill_point(model, cfg, pk: dict) -> dict:
     from research_2_b200.engine.step import StepFunction
 
     n_req, length = 2, 1024
-    step_fn = StepFunction(model, PAGE, n_req * length // PAGE, n_req, capture=True)  # a shape that repeats runs as a graph
-    cache = CacheManager(step_fn.cache_groups(), n_req, model.max_seq_len)
+    step_fn = StepFunction(model, PAGE, n_req * length // PAGE, n_req, capture=True,  # a shape that repeats runs as a graph
+                           max_seq_len=min(model.max_seq_len, CONTEXT))
+    cache = CacheManager(step_fn.cache_groups(), n_req, step_fn.max_seq_len)
     gen = torch.Generator().manual_seed(SEED + 1)
     prompts = torch.randint(0, model.vocab_size, (n_req, length), generator=gen, dtype=torch.int32).numpy()
     for r in range(n_req):
@@ -266,9 +274,110 @@ def prefill_point(model, cfg, pk: dict) -> dict:
         if it >= 2:
             times.append(start.elapsed_time(stop))
     ms = statistics.median(times)
-    d, f, layers, v, t = cfg.n_embd, cfg.n_inner, cfg.n_layer, cfg.vocab_size, n_req * length
-    flops = 2 * t * layers * (3 * d * d + d * d + 2 * d * f) + layers * n_req * 4 * d * length * (length + 1) / 2 + 2 * n_req * d * v
+    t = n_req * length
+    if hasattr(cfg, "n_embd"):
+        d, f, layers, v = cfg.n_embd, cfg.n_inner, cfg.n_layer, cfg.vocab_size
+        flops = 2 * t * layers * (3 * d * d + d * d + 2 * d * f) + layers * n_req * 4 * d * length * (length + 1) / 2 + 2 * n_req * d * v
+    else:
+        flops = gated_design_flops(cfg, n_req, length)
     return {"value": t / (ms / 1e3), "tokens": t, "ms": ms, "frac": flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12)}
+
+
+def gated_design_config(size: str, n_layer: int, kv_heads: int, window: int, keep_first: int) -> dict:
+    """A Zirunex configuration with the width, heads, head size, layers and vocabulary of a GPT-2 size. The gated
+    feed-forward has three matrices where GPT-2's has two: its inner width is 2/3 of GPT-2's (to a multiple of
+    128), so that both feed-forwards hold the same number of weights."""
+    g = SIZES[size]
+    d, h = g["n_embd"], g["n_head"]
+    mixer = {"heads": h, "kv_heads": kv_heads or h, "dim": d // h, "vdim": d // h, "scale": (d // h) ** -0.5,
+             "mask": {"size": window, "keep_first": keep_first}}
+    mlp = {"kind": "dense", "ff": max(128, round(2 * g["n_inner"] / 3 / 128) * 128), "limit": 7.0}
+    return {"architecture": "Zirunex", "vocab": g["vocab_size"], "width": d, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "layers": [{"type": "attention", "mixer": mixer, "mlp": mlp} for _ in range(n_layer)]}
+
+
+def gated_design_flops(cfg, n_req: int, length: int) -> float:
+    """Flops of one prefill step of n_req prompts of `length` tokens through a Zirunex configuration."""
+    t, total = n_req * length, 0.0
+    for layer in cfg.layers:
+        m = layer.mixer
+        q, kv, o = m.heads * m.dim, m.kv_heads * m.dim, m.heads * m.vdim
+        total += 2 * t * cfg.width * (q + kv + m.kv_heads * m.vdim + o) + 2 * t * o * cfg.width
+        if layer.mlp is not None:
+            total += 2 * t * cfg.width * 3 * layer.mlp.ff
+        pairs = sum(min(i + 1, m.window) + max(0, min(m.keep_first, i + 1 - m.window)) for i in range(length))
+        total += n_req * 2 * (q + o) * pairs
+    return total + 2 * n_req * cfg.width * cfg.vocab_size
+
+
+def build_gated_design(data: dict, dtype: str = "bfloat16"):
+    import torch
+    from research_2_b200 import models  # noqa: F401
+    from research_2_b200.config.registry import architecture_of
+    from research_2_b200.models.loading import compute_dtype
+    from research_2_b200.parts import Runtime
+
+    arch = architecture_of(data)
+    cfg = arch.parse_config(data)
+    tensors = {k: v.to(torch.bfloat16) for k, v in arch.random_weights(cfg, SEED, std=0.02).items()}
+    return arch.build(cfg, tensors, Runtime(torch.device("cuda:0"), compute_dtype(dtype))), cfg
+
+
+def design_points(args, pk: dict) -> dict:
+    """`--design zirunex`: prefill and decode throughput of Zirunex models with the layer sizes of `--model`, beside
+    GPT-2 of that size through the same loops, and the design's kernels one by one beside their likes."""
+    import torch
+    from research_2_b200.profiling import kernel_cases
+
+    g = SIZES[args.model]
+    variants = {
+        "gpt2": None,
+        # as many key/value heads as heads and a window that holds every key: the attention's work equals GPT-2's
+        "zirunex, every key seen": gated_design_config(args.model, args.layers, 0, CONTEXT, 0),
+        # what a model of this design looks like: grouped heads, a window, kept first tokens
+        "zirunex, 4 query heads a kv head, window 256 + 4 kept": gated_design_config(args.model, args.layers, max(1, g["n_head"] // 4), 256, 4),
+    }
+    out = {"design": "zirunex", "sizes_of": args.model, "layers": args.layers, "prompt_len": PROMPT_LEN, "models": {}}
+    for name, data in variants.items():
+        model, cfg = build_model(args.layers, size=args.model) if data is None else build_gated_design(data)
+        point = {}
+        for batch in (8, 64):
+            steps = min(args.steps, 96)
+            value, ms, loop, kv_bytes = decode_point(model, batch, steps, args.warmup)
+            achieved = (model.weight_bytes_per_step() + kv_bytes) / (ms / 1e3) / 1e9
+            point[f"decode_b{batch}"] = {"tokens/s": round(value), "ms_per_step": round(ms, 4), "kernels_per_step": loop.graph.kernels,
+                                         "hbm_frac": round(achieved / pk["hbm_gbs"], 3)}
+            del loop
+            torch.cuda.empty_cache()
+        pre = prefill_point(model, cfg, pk)
+        point["prefill_2x1024"] = {"tokens/s": round(pre["value"]), "ms": round(pre["ms"], 3), "bf16_frac": round(pre["frac"], 3)}
+        out["models"][name] = point
+        del model
+        torch.cuda.empty_cache()
+    inner = max(128, round(2 * g["n_inner"] / 3 / 128) * 128)
+    head_dim = g["n_embd"] // g["n_head"]
+    table = {}
+
+    def add(name, fn, n_bytes, flops):
+        us = kernel_cases.time_in_graph(fn)
+        if n_bytes:
+            table[name] = {"us": round(us, 2), "frac": round(n_bytes / us / 1e3 / pk["hbm_gbs"], 3), "of": "copy bandwidth"}
+        else:
+            table[name] = {"us": round(us, 2), "frac": round(flops / us / 1e6 / pk["bf16_tflops"], 3), "of": "bf16 peak"}
+
+    kernel_cases.configure(g["n_embd"], g["n_inner"], g["n_head"], head_dim, g["vocab_size"], PAGE)
+    for name, fn, n_bytes, flops in kernel_cases.cases(8):   # the likes among GPT-2's kernels
+        if (name.startswith("prefill: LayerNorm") or "attention with cache write" in name or "2 x 1,024 tokens" in name
+                or "64 decoded tokens beside" in name or name.startswith("prefill: qkv product, 2,048")
+                or name.startswith("prefill: fc product with gelu, 2,048") or name.startswith("decode: LayerNorm + qkv")):
+            add(name, fn, n_bytes, flops)
+    kernel_cases.configure(g["n_embd"], inner, g["n_head"], head_dim, g["vocab_size"], PAGE)
+    for kv_heads in (None, max(1, g["n_head"] // 4)):
+        for name, fn, n_bytes, flops in kernel_cases.gated_cases(8, kv_heads):
+            if kv_heads is None or "attention" in name:
+                add(name, fn, n_bytes, flops)
+    out["kernels"] = table
+    return out
 
 
 def e2e_point(model, batch: int, steps: int, warmup: int) -> dict:
@@ -444,6 +553,9 @@ def main() -> int:
     ap.add_argument("--phases", action="store_true", help="print where a layer's time goes inside the resident decode kernel at --batch rows, and stop")
     ap.add_argument("--logits-ctas", action="store_true", help="print when each CTA of a decode step's logits product starts and ends (its waves), and stop")
     ap.add_argument("--prefill", action="store_true", help="print the prefill point (2 x 1,024 tokens in one step) alone, and stop")
+    ap.add_argument("--design", default=None, choices=("zirunex",),
+                    help="print prefill and decode throughput of that design at the layer sizes of --model beside GPT-2's, "
+                         "and its kernels beside their likes, and stop (the default workload is GPT-2's)")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
@@ -475,6 +587,9 @@ def main() -> int:
     from research_2_b200.kernels import ops
 
     pk, pk_source = peaks()
+    if args.design:
+        print(json.dumps(design_points(args, pk)))
+        return 0
     model, cfg = build_model(args.layers, size=args.model)
     if args.phases:
         print(json.dumps(resident_phases(model, args.batch)))

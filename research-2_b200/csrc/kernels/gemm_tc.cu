@@ -224,7 +224,7 @@ __device__ __forceinline__ void tmem_load16(uint32_t taddr, uint32_t (&r)[16]) {
       : "memory");
 }
 
-// LayerNorm of the token rows, written as the K-major, 128-byte-swizzled bfloat16 tiles that the
+// LayerNorm (or, without a shift vector, RMS norm) of the token rows, written as the K-major, 128-byte-swizzled bfloat16 tiles that the
 // tensor core reads: warp `w` of the four takes rows w, w + 4, ...; a lane holds every 32nd group
 // of four elements of its row (rows of at most 1,024 elements, at most 16 tokens); mean and
 // variance are two passes over registers, in float
@@ -244,7 +244,7 @@ __device__ __forceinline__ void load_norm_weights(const GemmParams& p, int kb_be
     int k = (lane + 32 * i) * 4;
     bool mine = k >= k_lo && k < k_hi;
     gam[i] = mine ? __ldg(reinterpret_cast<const float4*>(p.ln_gamma + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
-    bet[i] = mine ? __ldg(reinterpret_cast<const float4*>(p.ln_beta + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    bet[i] = (mine && p.ln_beta != nullptr) ? __ldg(reinterpret_cast<const float4*>(p.ln_beta + k)) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
 }
 
@@ -292,7 +292,8 @@ __device__ __forceinline__ void build_normed_tokens(const GemmParams& p, uint8_t
       sum[1] += v[1][i].x + v[1][i].y + v[1][i].z + v[1][i].w;
     }
     warp_sum2(sum[0], sum[1]);
-    const float mean[2] = {sum[0] * inv_k, sum[1] * inv_k};
+    // without a shift vector the norm is an RMS norm: nothing is taken off the row, and sq is its mean square
+    const float mean[2] = {p.ln_beta != nullptr ? sum[0] * inv_k : 0.f, p.ln_beta != nullptr ? sum[1] * inv_k : 0.f};
     float sq[2] = {0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < LN_CHUNKS; ++i) {
@@ -1569,8 +1570,8 @@ extern "C" int r2_gemm_tc(const void* x, int lda, const void* w, int ldw, int w_
   if (m <= 0 || n <= 0) return R2_OK;
   const bool fused_ln = ln_x != nullptr;
   if (fused_ln) {
-    if (m > LN_MAX_TOKENS || k > LN_MAX_K || k % 8 != 0 || ln_ldx % 4 != 0 || ln_gamma == nullptr || ln_beta == nullptr) return R2_UNSUPPORTED;
-    if ((reinterpret_cast<uintptr_t>(ln_x) & 15) || (reinterpret_cast<uintptr_t>(ln_gamma) & 15) || (reinterpret_cast<uintptr_t>(ln_beta) & 15)) return R2_UNSUPPORTED;
+    if (m > LN_MAX_TOKENS || k > LN_MAX_K || k % 8 != 0 || ln_ldx % 4 != 0 || ln_gamma == nullptr) return R2_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(ln_x) & 15) || (reinterpret_cast<uintptr_t>(ln_gamma) & 15) || (reinterpret_cast<uintptr_t>(ln_beta) & 15)) return R2_UNSUPPORTED;  // (a null shift: RMS norm)
     x = w;  // only its alignment is looked at below
     lda = 8;
   }

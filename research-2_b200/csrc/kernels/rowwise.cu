@@ -212,6 +212,13 @@ extern "C" int r2_kv_write(const void* k_src, const void* v_src, int src_row_str
   return launch_status();
 }
 
+// Two neighbouring elements as one access (4 bytes of bfloat16, 8 of float).
+__device__ __forceinline__ float2 load2(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ float2 load2(const bf16* p) { return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p)); }
+__device__ __forceinline__ void store2(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void store2(bf16* p, float a, float b) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b); }
+template <typename T> __host__ __device__ inline bool pair_aligned(const T* p) { return (reinterpret_cast<uintptr_t>(p) & (2 * sizeof(T) - 1)) == 0; }
+
 // ---------------------------------------------------------------------------------------------
 // RMS norm: y = x / sqrt(mean(x^2) + eps) * (offset + w), statistics in float. `offset` is 1 for a
 // weight that is stored around zero and 0 for a plain gain. `rows` (may be null) picks input rows.
@@ -237,11 +244,62 @@ rms_norm_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows, c
   for (int d = lane; d < width; d += 32) o[d] = from_float<O>(xr[d] * inv * (offset + weight[d]));
 }
 
+// The same with the row in the warp's registers, read once in 16-byte pieces: rows of up to 2,048 elements
+// whose length is a multiple of 4.
+template <typename O>
+__global__ void __launch_bounds__(128)
+rms_norm_reg_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows, const float* __restrict__ weight,
+                    O* __restrict__ out, int n_rows, int width, float eps, float offset) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (r >= n_rows) return;
+  const int src = rows != nullptr ? rows[r] : r;
+  const float4* xr = reinterpret_cast<const float4*>(x + size_t(src) * width);
+  constexpr int CHUNKS = 2048 / 128;
+  float4 v[CHUNKS];
+  float sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < CHUNKS; ++i) {
+    const int k = (lane + 32 * i) * 4;
+    v[i] = k < width ? xr[lane + 32 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    sq += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+  }
+  const float inv = 1.f / sqrtf(warp_sum(sq) / float(width) + eps);
+  O* o = out + size_t(r) * width;
+#pragma unroll
+  for (int i = 0; i < CHUNKS; ++i) {
+    const int k = (lane + 32 * i) * 4;
+    if (k < width) {
+      const float4 g = *reinterpret_cast<const float4*>(weight + k);
+      const float y0 = v[i].x * inv * (offset + g.x), y1 = v[i].y * inv * (offset + g.y);
+      const float y2 = v[i].z * inv * (offset + g.z), y3 = v[i].w * inv * (offset + g.w);
+      if constexpr (sizeof(O) == 2) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(y0, y1), hi = __floats2bfloat162_rn(y2, y3);
+        *reinterpret_cast<uint2*>(o + k) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+      } else {
+        *reinterpret_cast<float4*>(o + k) = make_float4(y0, y1, y2, y3);
+      }
+    }
+  }
+}
+
 extern "C" int r2_rms_norm(const float* x, const int32_t* rows, const float* weight, void* out, int n_rows, int width,
                            float eps, float offset, int odtype, cudaStream_t stream) {
   if (n_rows <= 0) return R2_OK;
   if (width < 1) return R2_BAD_SHAPE;
   dim3 grid((n_rows + 3) / 4);
+  const bool aligned = width % 4 == 0 && width <= 2048 && !(reinterpret_cast<uintptr_t>(x) & 15) &&
+                       !(reinterpret_cast<uintptr_t>(weight) & 15) && !(reinterpret_cast<uintptr_t>(out) & 15);
+  if (aligned && odtype == R2_F32) {
+    r2_launch(rms_norm_reg_kernel<float>, grid, dim3(128), size_t(0), stream, x, rows, weight, (float*)out, n_rows, width, eps, offset);
+    return launch_status();
+  }
+  if (aligned && odtype == R2_BF16) {
+    r2_launch(rms_norm_reg_kernel<bf16>, grid, dim3(128), size_t(0), stream, x, rows, weight, (bf16*)out, n_rows, width, eps, offset);
+    return launch_status();
+  }
   if (odtype == R2_F32) {
     r2_launch(rms_norm_kernel<float>, grid, dim3(128), size_t(0), stream, x, rows, weight, (float*)out, n_rows, width, eps, offset);
   } else if (odtype == R2_BF16) {
@@ -256,17 +314,41 @@ extern "C" int r2_rms_norm(const float* x, const int32_t* rows, const float* wei
 // RMS norm of every head of the query and key columns of a fused projection, in place: the row's
 // first n_q_heads heads take the gain w_q, the n_k_heads heads after them w_k (both of head_dim
 // values, shared by all heads of their kind). One warp per (row, head), sums in float.
+// With a cache (k_cache not null) the same launch also puts the row's normed key heads and its value
+// heads (n_k_heads heads of v_head_dim values from column v_col on) into the row's cache slot, so that
+// no second kernel reads the projection again.
 template <typename T>
 __global__ void __launch_bounds__(128)
 head_norm_kernel(T* __restrict__ buf, int row_stride, int n_rows, int n_q_heads, int n_k_heads, int head_dim,
-                 const float* __restrict__ w_q, const float* __restrict__ w_k, float eps, float offset) {
+                 const float* __restrict__ w_q, const float* __restrict__ w_k, float eps, float offset,
+                 T* __restrict__ k_cache, T* __restrict__ v_cache, const int32_t* __restrict__ slot_mapping, int v_col,
+                 int v_head_dim, int page_size, long long page_stride, int n_pages) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
-  const int heads = n_q_heads + n_k_heads;
+  const int heads = n_q_heads + n_k_heads + (k_cache != nullptr ? n_k_heads : 0);
   const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
   if (item >= (long long)n_rows * heads) return;
   const int r = int(item / heads), h = int(item % heads);
+  size_t page_base = 0;   // where the slot's page begins in this layer's cache
+  int off = 0;            // the slot's place within the page
+  bool cached = false;
+  if (k_cache != nullptr && h >= n_q_heads) {
+    const int slot = slot_mapping[r];
+    const int page = slot / page_size;
+    cached = slot >= 0 && page < n_pages;  // slots are validated on the host; never write outside the pool
+    page_base = size_t(page) * page_stride;
+    off = slot % page_size;
+  }
+  if (h >= n_q_heads + n_k_heads) {  // a value head: copied as it is
+    const int vh = h - n_q_heads - n_k_heads;
+    const T* src = buf + size_t(r) * row_stride + v_col + size_t(vh) * v_head_dim;
+    if (cached) {
+      T* dst = v_cache + page_base + (size_t(vh) * page_size + off) * v_head_dim;
+      for (int d = lane; d < v_head_dim; d += 32) dst[d] = src[d];
+    }
+    return;
+  }
   T* p = buf + size_t(r) * row_stride + size_t(h) * head_dim;
   const float* w = h < n_q_heads ? w_q : w_k;
   float sq = 0.f;
@@ -275,19 +357,204 @@ head_norm_kernel(T* __restrict__ buf, int row_stride, int n_rows, int n_q_heads,
     sq = fmaf(v, v, sq);
   }
   const float inv = 1.f / sqrtf(warp_sum(sq) / float(head_dim) + eps);
-  for (int d = lane; d < head_dim; d += 32) p[d] = from_float<T>(to_float(p[d]) * inv * (offset + w[d]));
+  T* dst = nullptr;
+  if (cached) dst = k_cache + page_base + (size_t(h - n_q_heads) * page_size + off) * head_dim;
+  for (int d = lane; d < head_dim; d += 32) {
+    const T y = from_float<T>(to_float(p[d]) * inv * (offset + w[d]));
+    p[d] = y;
+    if (dst != nullptr) dst[d] = y;
+  }
+}
+
+// The same with a head in the warp's registers, two neighbouring elements per access: even head sizes up to
+// 512 in buffers and caches whose strides and starts are even.
+template <typename T>
+__global__ void __launch_bounds__(128)
+head_norm_pair_kernel(T* __restrict__ buf, int row_stride, int n_rows, int n_q_heads, int n_k_heads, int head_dim,
+                      const float* __restrict__ w_q, const float* __restrict__ w_k, float eps, float offset,
+                      T* __restrict__ k_cache, T* __restrict__ v_cache, const int32_t* __restrict__ slot_mapping, int v_col,
+                      int v_head_dim, int page_size, long long page_stride, int n_pages) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int heads = n_q_heads + n_k_heads + (k_cache != nullptr ? n_k_heads : 0);
+  const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (item >= (long long)n_rows * heads) return;
+  const int r = int(item / heads), h = int(item % heads);
+  size_t page_base = 0;
+  int off = 0;
+  bool cached = false;
+  if (k_cache != nullptr && h >= n_q_heads) {
+    const int slot = slot_mapping[r];
+    const int page = slot / page_size;
+    cached = slot >= 0 && page < n_pages;
+    page_base = size_t(page) * page_stride;
+    off = slot % page_size;
+  }
+  if (h >= n_q_heads + n_k_heads) {
+    const int vh = h - n_q_heads - n_k_heads;
+    const T* src = buf + size_t(r) * row_stride + v_col + size_t(vh) * v_head_dim;
+    if (cached) {
+      T* dst = v_cache + page_base + (size_t(vh) * page_size + off) * v_head_dim;
+      for (int d = 2 * lane; d < v_head_dim; d += 64) {
+        const float2 v = load2(src + d);
+        store2(dst + d, v.x, v.y);
+      }
+    }
+    return;
+  }
+  T* p = buf + size_t(r) * row_stride + size_t(h) * head_dim;
+  const float* w = h < n_q_heads ? w_q : w_k;
+  float2 v[8];
+  float sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int d = 2 * lane + 64 * i;
+    v[i] = d < head_dim ? load2(p + d) : make_float2(0.f, 0.f);
+    sq += v[i].x * v[i].x + v[i].y * v[i].y;
+  }
+  const float inv = 1.f / sqrtf(warp_sum(sq) / float(head_dim) + eps);
+  T* dst = cached ? k_cache + page_base + (size_t(h - n_q_heads) * page_size + off) * head_dim : nullptr;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int d = 2 * lane + 64 * i;
+    if (d < head_dim) {
+      const float2 g = *reinterpret_cast<const float2*>(w + d);
+      // rounded once: the buffer and the cache hold the same values
+      const T y0 = from_float<T>(v[i].x * inv * (offset + g.x)), y1 = from_float<T>(v[i].y * inv * (offset + g.y));
+      store2(p + d, to_float(y0), to_float(y1));
+      if (dst != nullptr) store2(dst + d, to_float(y0), to_float(y1));
+    }
+  }
+}
+
+// The same for head sizes up to 128 with eight heads of a row per warp: all their loads are issued before
+// the first sum, so that a launch of many rows is bound by bandwidth and not by one round trip per head.
+template <typename T>
+__global__ void __launch_bounds__(128)
+head_norm_batch_kernel(T* __restrict__ buf, int row_stride, int n_rows, int n_q_heads, int n_k_heads, int head_dim,
+                       const float* __restrict__ w_q, const float* __restrict__ w_k, float eps, float offset,
+                       T* __restrict__ k_cache, T* __restrict__ v_cache, const int32_t* __restrict__ slot_mapping, int v_col,
+                       int v_head_dim, int page_size, long long page_stride, int n_pages) {
+  pdl_launch_dependents();
+  pdl_wait();
+  constexpr int U = 8;
+  const int lane = threadIdx.x & 31;
+  const int heads = n_q_heads + n_k_heads + (k_cache != nullptr ? n_k_heads : 0);
+  const int groups = (heads + U - 1) / U;
+  const int w = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (w >= n_rows * groups) return;
+  const int r = w / groups, h0 = (w % groups) * U;
+  T* row = buf + size_t(r) * row_stride;
+  size_t page_base = 0;
+  int off = 0;
+  bool cached = false;
+  if (k_cache != nullptr && h0 + U > n_q_heads) {
+    const int slot = slot_mapping[r];
+    const int page = slot / page_size;
+    cached = slot >= 0 && page < n_pages;
+    page_base = size_t(page) * page_stride;
+    off = slot % page_size;
+  }
+  // where head h0 + u begins in the row, and how long it is (a value head may have a size of its own)
+  float2 v[U][2];
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const int h = h0 + u;
+    const bool value = h >= n_q_heads + n_k_heads;
+    const int len = h < heads ? (value ? v_head_dim : head_dim) : 0;
+    const T* src = value ? row + v_col + size_t(h - n_q_heads - n_k_heads) * v_head_dim : row + size_t(h) * head_dim;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int d = 2 * lane + 64 * i;
+      v[u][i] = d < len ? load2(src + d) : make_float2(0.f, 0.f);
+    }
+  }
+  float sq[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) sq[u] = v[u][0].x * v[u][0].x + v[u][0].y * v[u][0].y + v[u][1].x * v[u][1].x + v[u][1].y * v[u][1].y;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) sq[u] += __shfl_xor_sync(0xffffffffu, sq[u], o);
+  }
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const int h = h0 + u;
+    if (h >= heads) break;
+    if (h >= n_q_heads + n_k_heads) {  // a value head: copied as it is
+      if (cached) {
+        T* dst = v_cache + page_base + (size_t(h - n_q_heads - n_k_heads) * page_size + off) * v_head_dim;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int d = 2 * lane + 64 * i;
+          if (d < v_head_dim) store2(dst + d, v[u][i].x, v[u][i].y);
+        }
+      }
+      continue;
+    }
+    const float inv = 1.f / sqrtf(sq[u] / float(head_dim) + eps);
+    const float* gain = h < n_q_heads ? w_q : w_k;
+    T* p = row + size_t(h) * head_dim;
+    T* dst = (cached && h >= n_q_heads) ? k_cache + page_base + (size_t(h - n_q_heads) * page_size + off) * head_dim : nullptr;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int d = 2 * lane + 64 * i;
+      if (d < head_dim) {
+        const float2 g = *reinterpret_cast<const float2*>(gain + d);
+        const T y0 = from_float<T>(v[u][i].x * inv * (offset + g.x)), y1 = from_float<T>(v[u][i].y * inv * (offset + g.y));
+        store2(p + d, to_float(y0), to_float(y1));
+        if (dst != nullptr) store2(dst + d, to_float(y0), to_float(y1));
+      }
+    }
+  }
 }
 
 extern "C" int r2_head_norm(void* buf, int row_stride, int n_rows, int n_q_heads, int n_k_heads, int head_dim,
-                            const float* w_q, const float* w_k, float eps, float offset, int dtype, cudaStream_t stream) {
+                            const float* w_q, const float* w_k, float eps, float offset, void* k_cache, void* v_cache,
+                            const int32_t* slot_mapping, int v_col, int v_head_dim, int page_size, long long page_stride,
+                            int n_pages, int dtype, cudaStream_t stream) {
   if (n_rows <= 0) return R2_OK;
   if (n_q_heads < 0 || n_k_heads < 0 || n_q_heads + n_k_heads < 1 || head_dim < 1) return R2_BAD_SHAPE;
-  const long long items = (long long)n_rows * (n_q_heads + n_k_heads);
+  if (k_cache != nullptr && (v_cache == nullptr || slot_mapping == nullptr || v_head_dim < 1 || page_size < 1 || n_pages < 1)) return R2_BAD_SHAPE;
+  const long long items = (long long)n_rows * (n_q_heads + n_k_heads + (k_cache != nullptr ? n_k_heads : 0));
   dim3 grid((unsigned)((items + 3) / 4));
+  const size_t esize = dtype == R2_F32 ? 4 : 2;
+  auto even = [&](const void* p) { return (reinterpret_cast<uintptr_t>(p) & (2 * esize - 1)) == 0; };
+  const bool pairs = head_dim % 2 == 0 && head_dim <= 512 && row_stride % 2 == 0 && even(buf) && even(w_q) && even(w_k) &&
+                     !(reinterpret_cast<uintptr_t>(w_q) & 7) && !(reinterpret_cast<uintptr_t>(w_k) & 7) &&
+                     (k_cache == nullptr || (v_col % 2 == 0 && v_head_dim % 2 == 0 && page_stride % 2 == 0 && even(k_cache) && even(v_cache)));
+  if (pairs && head_dim <= 128 && (k_cache == nullptr || v_head_dim <= 128)) {
+    const int heads = n_q_heads + n_k_heads + (k_cache != nullptr ? n_k_heads : 0);
+    const long long warps = (long long)n_rows * ((heads + 7) / 8);
+    dim3 bgrid((unsigned)((warps + 3) / 4));
+    if (dtype == R2_F32) {
+      r2_launch(head_norm_batch_kernel<float>, bgrid, dim3(128), size_t(0), stream, (float*)buf, row_stride, n_rows, n_q_heads, n_k_heads, head_dim, w_q, w_k, eps, offset,
+                (float*)k_cache, (float*)v_cache, slot_mapping, v_col, v_head_dim, page_size, page_stride, n_pages);
+      return launch_status();
+    }
+    if (dtype == R2_BF16) {
+      r2_launch(head_norm_batch_kernel<bf16>, bgrid, dim3(128), size_t(0), stream, (bf16*)buf, row_stride, n_rows, n_q_heads, n_k_heads, head_dim, w_q, w_k, eps, offset,
+                (bf16*)k_cache, (bf16*)v_cache, slot_mapping, v_col, v_head_dim, page_size, page_stride, n_pages);
+      return launch_status();
+    }
+  }
+  if (pairs && dtype == R2_F32) {
+    r2_launch(head_norm_pair_kernel<float>, grid, dim3(128), size_t(0), stream, (float*)buf, row_stride, n_rows, n_q_heads, n_k_heads, head_dim, w_q, w_k, eps, offset,
+              (float*)k_cache, (float*)v_cache, slot_mapping, v_col, v_head_dim, page_size, page_stride, n_pages);
+    return launch_status();
+  }
+  if (pairs && dtype == R2_BF16) {
+    r2_launch(head_norm_pair_kernel<bf16>, grid, dim3(128), size_t(0), stream, (bf16*)buf, row_stride, n_rows, n_q_heads, n_k_heads, head_dim, w_q, w_k, eps, offset,
+              (bf16*)k_cache, (bf16*)v_cache, slot_mapping, v_col, v_head_dim, page_size, page_stride, n_pages);
+    return launch_status();
+  }
   if (dtype == R2_F32) {
-    r2_launch(head_norm_kernel<float>, grid, dim3(128), size_t(0), stream, (float*)buf, row_stride, n_rows, n_q_heads, n_k_heads, head_dim, w_q, w_k, eps, offset);
+    r2_launch(head_norm_kernel<float>, grid, dim3(128), size_t(0), stream, (float*)buf, row_stride, n_rows, n_q_heads, n_k_heads, head_dim, w_q, w_k, eps, offset,
+              (float*)k_cache, (float*)v_cache, slot_mapping, v_col, v_head_dim, page_size, page_stride, n_pages);
   } else if (dtype == R2_BF16) {
-    r2_launch(head_norm_kernel<bf16>, grid, dim3(128), size_t(0), stream, (bf16*)buf, row_stride, n_rows, n_q_heads, n_k_heads, head_dim, w_q, w_k, eps, offset);
+    r2_launch(head_norm_kernel<bf16>, grid, dim3(128), size_t(0), stream, (bf16*)buf, row_stride, n_rows, n_q_heads, n_k_heads, head_dim, w_q, w_k, eps, offset,
+              (bf16*)k_cache, (bf16*)v_cache, slot_mapping, v_col, v_head_dim, page_size, page_stride, n_pages);
   } else {
     return R2_BAD_DTYPE;
   }
@@ -313,11 +580,68 @@ gated_act_kernel(const T* __restrict__ gate_up, int in_stride, T* __restrict__ o
   }
 }
 
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_act_pair_kernel(const T* __restrict__ gate_up, int in_stride, T* __restrict__ out, int out_stride, int inner,
+                      float limit, float alpha, float up_offset) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const T* in = gate_up + size_t(blockIdx.x) * in_stride;
+  T* o = out + size_t(blockIdx.x) * out_stride;
+  for (int f = 2 * (blockIdx.y * blockDim.x + threadIdx.x); f < inner; f += 2 * gridDim.y * blockDim.x) {
+    const float2 gv = load2(in + f), uv = load2(in + inner + f);
+    const float g0 = fminf(gv.x, limit), g1 = fminf(gv.y, limit);
+    const float u0 = fminf(fmaxf(uv.x, -limit), limit), u1 = fminf(fmaxf(uv.y, -limit), limit);
+    store2(o + f, g0 / (1.f + expf(-alpha * g0)) * (u0 + up_offset), g1 / (1.f + expf(-alpha * g1)) * (u1 + up_offset));
+  }
+}
+
+// bfloat16 rows whose halves start on 16-byte boundaries: eight outputs per thread from two 16-byte loads.
+__global__ void __launch_bounds__(256)
+gated_act_vec8_kernel(const bf16* __restrict__ gate_up, int in_stride, bf16* __restrict__ out, int out_stride, int inner,
+                      float limit, float alpha, float up_offset) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const bf16* in = gate_up + size_t(blockIdx.x) * in_stride;
+  bf16* o = out + size_t(blockIdx.x) * out_stride;
+  for (int f = 8 * (blockIdx.y * blockDim.x + threadIdx.x); f < inner; f += 8 * gridDim.y * blockDim.x) {
+    const uint4 gq = *reinterpret_cast<const uint4*>(in + f), uq = *reinterpret_cast<const uint4*>(in + inner + f);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gq);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uq);
+    uint4 yq;
+    __nv_bfloat162* y2 = reinterpret_cast<__nv_bfloat162*>(&yq);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 gv = __bfloat1622float2(g2[i]), uv = __bfloat1622float2(u2[i]);
+      const float g0 = fminf(gv.x, limit), g1 = fminf(gv.y, limit);
+      const float u0 = fminf(fmaxf(uv.x, -limit), limit), u1 = fminf(fmaxf(uv.y, -limit), limit);
+      y2[i] = __floats2bfloat162_rn(g0 / (1.f + expf(-alpha * g0)) * (u0 + up_offset), g1 / (1.f + expf(-alpha * g1)) * (u1 + up_offset));
+    }
+    *reinterpret_cast<uint4*>(o + f) = yq;
+  }
+}
+
 extern "C" int r2_gated_act(const void* gate_up, int in_stride, void* out, int out_stride, int n_rows, int inner, float limit,
                             float alpha, float up_offset, int dtype, cudaStream_t stream) {
   if (n_rows <= 0) return R2_OK;
   if (inner < 1) return R2_BAD_SHAPE;
   dim3 grid(n_rows, (inner + 1023) / 1024);
+  const size_t esize = dtype == R2_F32 ? 4 : 2;
+  const bool pairs = inner % 2 == 0 && in_stride % 2 == 0 && out_stride % 2 == 0 &&
+                     !(reinterpret_cast<uintptr_t>(gate_up) & (2 * esize - 1)) && !(reinterpret_cast<uintptr_t>(out) & (2 * esize - 1));
+  if (dtype == R2_BF16 && inner % 8 == 0 && in_stride % 8 == 0 && out_stride % 8 == 0 &&
+      !(reinterpret_cast<uintptr_t>(gate_up) & 15) && !(reinterpret_cast<uintptr_t>(out) & 15)) {
+    r2_launch(gated_act_vec8_kernel, dim3(n_rows, (inner + 2047) / 2048), dim3(256), size_t(0), stream, (const bf16*)gate_up, in_stride, (bf16*)out, out_stride, inner, limit, alpha, up_offset);
+    return launch_status();
+  }
+  if (pairs && dtype == R2_F32) {
+    r2_launch(gated_act_pair_kernel<float>, dim3(n_rows, (inner + 511) / 512), dim3(256), size_t(0), stream, (const float*)gate_up, in_stride, (float*)out, out_stride, inner, limit, alpha, up_offset);
+    return launch_status();
+  }
+  if (pairs && dtype == R2_BF16) {
+    r2_launch(gated_act_pair_kernel<bf16>, dim3(n_rows, (inner + 511) / 512), dim3(256), size_t(0), stream, (const bf16*)gate_up, in_stride, (bf16*)out, out_stride, inner, limit, alpha, up_offset);
+    return launch_status();
+  }
   if (dtype == R2_F32) {
     r2_launch(gated_act_kernel<float>, grid, dim3(256), size_t(0), stream, (const float*)gate_up, in_stride, (float*)out, out_stride, inner, limit, alpha, up_offset);
   } else if (dtype == R2_BF16) {

@@ -426,17 +426,23 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch
 
 
 def head_norm(buf: torch.Tensor, n_q_heads: int, n_k_heads: int, head_dim: int, w_q: torch.Tensor, w_k: torch.Tensor,
-              eps: float, unit_offset: bool = False) -> None:
+              eps: float, unit_offset: bool = False, kv: KvScatter | None = None) -> None:
     """RMS norm, in place, of each of the first n_q_heads + n_k_heads heads of every row of `buf` (a fused
     projection whose first columns are the query heads and then the key heads); the query heads take the
-    gain `w_q`, the key heads `w_k` (float32 [head_dim], shared by the heads of a kind)."""
+    gain `w_q`, the key heads `w_k` (float32 [head_dim], shared by the heads of a kind). With `kv` (see
+    `kv_scatter`; `col` the first value column, `width` the values' width, `head_dim` the values' head size)
+    the same launch puts the normed keys and the values into the rows' cache slots."""
     _need(buf, "buf", dim=2)
     _need(w_q, "w_q", torch.float32, 1)
     _need(w_k, "w_k", torch.float32, 1)
     if w_q.shape[0] != head_dim or w_k.shape[0] != head_dim or buf.shape[1] < (n_q_heads + n_k_heads) * head_dim:
         raise KernelError(f"head_norm: buf {tuple(buf.shape)} does not hold {n_q_heads} + {n_k_heads} heads of {head_dim}")
+    if kv is not None and (kv.width != n_k_heads * kv.head_dim or kv.col + kv.width > buf.shape[1]):
+        raise KernelError("head_norm: the value columns do not fit the projection")
+    cache = (C.c_void_p(kv.k_cache), C.c_void_p(kv.v_cache), C.c_void_p(kv.slots), kv.col, kv.head_dim, kv.page_size,
+             C.c_longlong(kv.page_stride), kv.n_pages) if kv is not None else (None, None, None, 0, 0, 0, C.c_longlong(0), 0)
     status = _lib("rowwise").r2_head_norm(_p(buf), _rows(buf, "buf"), buf.shape[0], n_q_heads, n_k_heads, head_dim, _p(w_q),
-                                         _p(w_k), C.c_float(eps), C.c_float(1.0 if unit_offset else 0.0),
+                                         _p(w_k), C.c_float(eps), C.c_float(1.0 if unit_offset else 0.0), *cache,
                                          dtype_code(buf.dtype), _stream())
     _check(status, "head_norm")
 
@@ -459,15 +465,18 @@ def gated_act(gate_up: torch.Tensor, limit: float, alpha: float, up_offset: floa
 
 class NormedRows:
     """LayerNorm of float32 rows that has not been computed yet: `linear` may compute it inside
-    its own kernel (few rows, bfloat16), or `materialize()` runs the LayerNorm kernel."""
+    its own kernel (few rows, bfloat16), or `materialize()` runs the LayerNorm kernel. With `beta`
+    None it is an RMS norm with the gain `gamma`."""
 
-    def __init__(self, x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: float, dtype: torch.dtype,
+    def __init__(self, x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor | None, eps: float, dtype: torch.dtype,
                  rows: torch.Tensor | None = None):
         self.x, self.gamma, self.beta, self.eps, self.dtype, self.rows = x, gamma, beta, eps, dtype, rows
         self.shape = (x.shape[0] if rows is None else rows.shape[0], x.shape[1])
         self.device = x.device
 
     def materialize(self) -> torch.Tensor:
+        if self.beta is None:
+            return rms_norm(self.x, self.gamma, self.eps, self.dtype, rows=self.rows)
         return layer_norm(self.x, self.gamma, self.beta, self.eps, self.dtype, rows=self.rows)
 
 

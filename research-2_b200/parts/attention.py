@@ -150,15 +150,30 @@ class QKNormAttention:
     capturable = True
 
     def forward(self, h, residual, ctx, cache, state=None, writes_cache: bool = True):
-        proj = ops.linear(h, self.w_in, None, w_is_nk=True)
-        ops.head_norm(proj, self.n_heads, self.n_kv_heads, self.head_dim, self.q_norm, self.k_norm, self.norm_eps,
-                      self.norm_unit_offset)
+        return self.forward_projected(ops.linear(h, self.w_in, None, w_is_nk=True), residual, ctx, cache, state, writes_cache)
+
+    def input_matrix(self):
+        """The stacked projections of the mixer's input, [q; k; v; gate] x D stored [out, in]: a block whose
+        parts all read one normed input may run them as one product and call `forward_projected`."""
+        return self.w_in
+
+    def forward_projected(self, proj, residual, ctx, cache, state=None, writes_cache: bool = True):
+        """`proj` [T, q + k + v (+ gate) columns]: the input's projections, not yet normed."""
         at = self.q_width
         q, k = proj[:, :at], proj[:, at: at + self.k_width]
         at += self.k_width
         v = proj[:, at: at + self.v_width]
-        gate = proj[:, at + self.v_width:] if self.gated else None
-        if writes_cache and ctx.decode_only and self.v_head_dim == self.head_dim:
+        gate = proj[:, at + self.v_width: at + self.v_width + self.o_width] if self.gated else None
+        fused_decode = writes_cache and ctx.decode_only and self.v_head_dim == self.head_dim
+        # the norms work in place; where the attention kernel does not write the cache itself, the same launch
+        # puts the normed keys and the values into the rows' slots
+        scatter = None
+        if writes_cache and not fused_decode:
+            scatter = ops.kv_scatter(ctx.slot_mapping[cache.group], cache.k, cache.v, cache.page_stride, cache.page_size,
+                                     cache.n_pages, at, self.v_width, self.v_head_dim)
+        ops.head_norm(proj, self.n_heads, self.n_kv_heads, self.head_dim, self.q_norm, self.k_norm, self.norm_eps,
+                      self.norm_unit_offset, kv=scatter)
+        if fused_decode:
             # one new token per row: the kernel puts the new key and value into the cache itself
             mixed = ops.decode_attention_fused(
                 q, k, v, ctx.slot_mapping[cache.group], cache.k, cache.v, cache.page_stride, cache.page_size,
@@ -167,7 +182,6 @@ class QKNormAttention:
                 sink=self.sink, gate=gate, exact_weights=ops.exact_weights())
             if mixed is not None:
                 return ops.linear(mixed, self.w_out, None, w_is_nk=True, residual=residual)
-        if writes_cache:
             ops.kv_write(k, v, cache.k, cache.v, ctx.slot_mapping[cache.group], self.n_kv_heads, self.head_dim,
                          cache.page_size, cache.page_stride, cache.n_pages, v_head_dim=self.v_head_dim)
         mixed = ops.paged_attention(

@@ -2,6 +2,9 @@
 
 from __future__ import annotations
 
+import torch
+
+from ..kernels import ops
 from .base import register_block
 
 
@@ -52,8 +55,27 @@ class ParallelBlock:
             raise ValueError("a parallel block has one norm")
         self.norm_1, self.mixer, self.norm_2, self.feed_forward = norm_1, mixer, None, feed_forward
         self.compute_dtype = compute_dtype
+        # Both sublayers read the same h: where each offers the stacked matrix of its input projections
+        # (`input_matrix` / `forward_projected`), the block runs them as ONE product over both stacks. The
+        # parts keep views into the joint matrix, so they still work on their own.
+        self.w_in = None
+        ask = [getattr(p, "input_matrix", None) for p in (mixer, feed_forward)]
+        if feed_forward is not None and all(ask):
+            a, b = ask[0](), ask[1]()
+            if a.dtype == b.dtype and a.shape[1] == b.shape[1] and a.device == b.device:
+                self.w_in = torch.cat([a, b], dim=0)
+                self.split = a.shape[0]
+                mixer.w_in, feed_forward.w_gate_up = self.w_in[: self.split], self.w_in[self.split:]
 
     def forward(self, x, ctx, cache=None, state=None, writes_cache: bool = True):
+        if self.w_in is not None:
+            # (the norm stays a kernel of its own: inside the joint product's kernel, where every CTA of a product
+            # several thousand columns wide normalises the rows again, a decode step of 8 rows measured 0.48 ms
+            # against 0.39)
+            h = self.norm_1.forward(x, self.compute_dtype)
+            proj = ops.linear(h, self.w_in, None, w_is_nk=True)
+            x = self.mixer.forward_projected(proj[:, : self.split], x, ctx, cache, state, writes_cache)
+            return self.feed_forward.forward_projected(proj[:, self.split:], x, ctx)
         h = self.norm_1.forward(x, self.compute_dtype)
         x = self.mixer.forward(h, x, ctx, cache, state, writes_cache)
         if self.feed_forward is not None:

@@ -60,7 +60,14 @@ class GatedClampedMLP:
     def matrices(self):
         return [self.w_gate_up, self.w_down]
 
+    def input_matrix(self):
+        """The stacked projections of the input, [gate; up] x D stored [out, in] (see `forward_projected`)."""
+        return self.w_gate_up
+
     def forward(self, h, residual, ctx):
-        gate_up = ops.linear(h, self.w_gate_up, None, w_is_nk=True)
+        return self.forward_projected(ops.linear(h, self.w_gate_up, None, w_is_nk=True), residual, ctx)
+
+    def forward_projected(self, gate_up, residual, ctx):
+        """`gate_up` [T, 2 F]: the input's gate and up projections."""
         y = ops.gated_act(gate_up, self.limit, self.alpha, self.up_offset)
         return ops.linear(y, self.w_down, None, w_is_nk=True, residual=residual)

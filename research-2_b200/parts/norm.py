@@ -36,12 +36,17 @@ class RMSNorm:
     """x / sqrt(mean(x^2) + eps) * gain. params: eps; unit_offset (the stored weight lies around zero and the
     gain is 1 + weight; default false: the weight is the gain). weights: weight."""
 
-    can_be_lazy = False
+    can_be_lazy = True
 
     def __init__(self, params: dict, weights: dict, rt: Runtime):
         self.eps = float(params["eps"])
         self.unit_offset = bool(params.get("unit_offset", False))
-        self.weight = vector(weights["weight"], rt)
+        weight = vector(weights["weight"], rt)
+        self.gain = weight + 1.0 if self.unit_offset else weight   # in float32, as the kernels would add it
 
     def forward(self, x, out_dtype, rows=None, lazy: bool = False):
-        return ops.rms_norm(x, self.weight, self.eps, out_dtype, rows=rows, unit_offset=self.unit_offset)
+        """Normalised rows in out_dtype. With `lazy` the result is an `ops.NormedRows` that a following
+        `ops.linear` may compute inside its own kernel."""
+        if lazy:
+            return ops.NormedRows(x, self.gain, None, self.eps, out_dtype, rows=rows)
+        return ops.rms_norm(x, self.gain, self.eps, out_dtype, rows=rows)

@@ -146,6 +146,94 @@ def cases(rows: int = 8):
     return out
 
 
+def gated_cases(rows: int = 8, kv_heads: int | None = None, window: int = 256, keep_first: int = 4):
+    """The kernels that a layer of RMS norms, query/key norms, attention with a sink, kept first keys and an
+    output gate, and a gated clamped feed-forward runs, at the configured sizes (`F` is the gated unit's inner
+    width): (name, function, bytes, flops) like `cases`. Each stands beside its like in `cases`: the RMS norm
+    beside the LayerNorm, attention beside the plain kernels at the same shapes (first with a window that
+    holds every key, so that the work is equal; then with `window` and `keep_first`)."""
+    torch.manual_seed(1)
+    G = kv_heads or H
+    Q, KV = H * HD, G * HD
+    out = []
+    r2k = torch.randn(2048, D, device=dev)
+    w = torch.zeros(D, device=dev)
+    n_out = torch.empty(2048, D, device=dev, dtype=torch.bfloat16)
+    out.append((f"prefill: RMS norm, 2,048 x {D:,}", lambda: ops.rms_norm(r2k, w, 1e-5, torch.bfloat16, unit_offset=True, out=n_out), 2048 * D * 6, 0))
+    # the joint product of a layer's input projections [q; k; v; gate; ff gate; ff up]
+    n_in = 2 * Q + 2 * KV + 2 * F
+    x = torch.randn(2048, D, device=dev).bfloat16()
+    w_in = (torch.randn(n_in, D, device=dev) * 0.02).bfloat16()
+    out.append((f"prefill: joint input product, 2,048 x {D:,} x {n_in:,}", lambda: ops.linear(x, w_in, None, w_is_nk=True), 0, 2 * 2048 * D * n_in))
+    xr = x[:rows].contiguous()
+    out.append((f"decode: joint input product, {rows} x {D:,} x {n_in:,}", lambda: ops.linear(xr, w_in, None, w_is_nk=True), w_in.numel() * 2, 2 * rows * D * n_in))
+    proj = torch.randn(2048, n_in, device=dev).bfloat16()
+    gq, gk = torch.ones(HD, device=dev), torch.ones(HD, device=dev)
+    kc, vc, tables2, stride2, pages2 = paged(2) if G == H else (None,) * 5
+    if kc is not None:
+        slots2 = torch.arange(PS, PS + 2048, dtype=torch.int32, device=dev)
+        scatter = ops.kv_scatter(slots2, kc, vc, stride2, PS, pages2, Q + KV, KV, HD)
+        out.append((f"prefill: query/key norms with cache write, 2,048 x ({H} + {G}) heads of {HD}",
+                    lambda: ops.head_norm(proj, H, G, HD, gq, gk, 1e-5, kv=scatter), 2048 * (2 * (Q + KV) + 3 * KV) * 2, 0))
+    act_out = torch.empty(2048, F, device=dev, dtype=torch.bfloat16)
+    out.append((f"prefill: gated unit, 2,048 x {F:,}", lambda: ops.gated_act(proj[:, n_in - 2 * F:], 2.0, 1.702, 1.0, out=act_out), 2048 * 3 * F * 2, 0))
+
+    def pool(batch):
+        n_pages = batch * (1024 // PS) + 1
+        page_stride = 2 * G * PS * HD
+        mem = torch.randn(n_pages, page_stride, device=dev).bfloat16().view(-1)
+        tables = torch.arange(1, n_pages, dtype=torch.int32, device=dev).view(batch, 1024 // PS).contiguous()
+        return mem, mem[G * PS * HD:], tables, page_stride, n_pages
+
+    for batch, ctx_len in sorted({(rows, 768), (64, 640)}):
+        for win, keep in ((0, 0), (window, keep_first)):
+            kc, vc, tables, page_stride, n_pages = pool(batch)
+            qkvg = torch.randn(batch, 2 * Q + 2 * KV, device=dev).bfloat16()
+            row_ids = torch.arange(batch, dtype=torch.int32, device=dev)
+            pos = torch.full((batch,), ctx_len - 1, dtype=torch.int32, device=dev)
+            lens = torch.full((batch,), ctx_len, dtype=torch.int32, device=dev)
+            slots = (tables[:, (ctx_len - 1) // PS] * PS + (ctx_len - 1) % PS).to(torch.int32)
+            seen = ctx_len if win == 0 else min(ctx_len, win + keep)
+            what = "every key" if win == 0 else f"window {win} + {keep} kept"
+            out.append((f"decode: gated sink attention with cache write, {batch} rows x {H} heads ({G} kv), context {ctx_len}, {what}",
+                        lambda qkvg=qkvg, slots=slots, kc=kc, vc=vc, page_stride=page_stride, n_pages=n_pages, tables=tables, row_ids=row_ids,
+                        pos=pos, lens=lens, win=win, keep=keep: ops.decode_attention_fused(
+                            qkvg[:, :Q], qkvg[:, Q: Q + KV], qkvg[:, Q + KV: Q + 2 * KV], slots, kc, vc, page_stride, PS, n_pages, tables,
+                            row_ids, pos, lens, H, G, HD, HD**-0.5, win, 1024, keep_first=keep, sink=True, gate=qkvg[:, Q + 2 * KV:],
+                            exact_weights=True),
+                        batch * seen * 2 * KV * 2, 4 * batch * seen * Q))
+
+    def attention_case(name, entries, win, keep):
+        batch = len(entries)
+        rows_ = [r for r, _ in entries]
+        kc, vc, tables, page_stride, n_pages = pool(batch)
+        n = sum(rows_)
+        q = torch.randn(n, Q, device=dev).bfloat16()
+        gate = torch.randn(n, Q, device=dev).bfloat16()
+        row_entry = torch.cat([torch.full((r,), e, dtype=torch.int32) for e, r in enumerate(rows_)]).to(dev)
+        positions = torch.cat([torch.arange(length - r, length, dtype=torch.int32) for r, length in entries]).to(dev)
+        lens = torch.tensor([length for _, length in entries], dtype=torch.int32, device=dev)
+        q_start = torch.tensor([sum(rows_[:i]) for i in range(batch + 1)], dtype=torch.int32, device=dev)
+        n_tiles = sum((r + 63) // 64 for r in rows_)
+
+        def pairs(r, length):   # (query, key) pairs that the mask lets through
+            total = 0
+            for i in range(length - r, length):
+                total += min(i + 1, win) + max(0, min(keep, i + 1 - win)) if win > 0 else i + 1
+            return total
+
+        flops = sum(4 * Q * pairs(r, length) for r, length in entries)
+        what = "every key" if win == 0 else f"window {win} + {keep} kept"
+        out.append((f"prefill gated sink attention on mma.sync, {name} x {H} heads ({G} kv), {what}",
+                    lambda: ops.paged_attention(q, kc, vc, page_stride, PS, n_pages, tables, row_entry, positions, lens, H, G, HD, HD**-0.5,
+                                                win, q_start=q_start, n_tiles=n_tiles, keep_first=keep, sink=True, gate=gate), 0, flops))
+
+    for win, keep in ((0, 0), (window, keep_first)):
+        attention_case("2 x 1,024 tokens", [(1024, 1024)] * 2, win, keep)
+        attention_case("64 decoded tokens beside a portion of 448", [(1, 600 + i) for i in range(64)] + [(448, 704)], win, keep)
+    return out
+
+
 def time_in_graph(fn, launches=20) -> float:
     for _ in range(3):
         fn()
@@ -208,10 +296,12 @@ def main(argv):
     ap.add_argument("--case", default="", help="keep the cases whose name contains this text")
     ap.add_argument("--list", action="store_true")
     ap.add_argument("--time", action="store_true")
+    ap.add_argument("--gated", action="store_true", help="the cases of a layer with RMS norms, gated sink attention and a gated feed-forward (--inner is the gated unit's width)")
+    ap.add_argument("--kv-heads", type=int, default=0, help="with --gated: key/value heads (0: as many as heads)")
     ap.add_argument("--ctas", action="store_true", help="for a case that is one tensor-core product (single-CTA form): when each of its CTAs starts and ends")
     args = ap.parse_args(argv)
     configure(args.width, args.inner, args.heads, args.head_dim, args.vocab, args.page_size)
-    for name, fn, n_bytes, flops in cases(args.rows):
+    for name, fn, n_bytes, flops in (gated_cases(args.rows, args.kv_heads or None) if args.gated else cases(args.rows)):
         if args.case not in name:
             continue
         if args.list:
