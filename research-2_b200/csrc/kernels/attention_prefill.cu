@@ -54,7 +54,7 @@ struct PrefillParams {
   int n_heads, n_kv_heads;
   float scale; int window;
   // With a window, an entry's first `keep_first` keys stay visible beside the window's. `sink` adds one to
-  // every softmax's denominator (a key of score 0 that has no value). `gate` (may be null;
+  // every softmax's denominator (an extra exp(0) term). `gate` (may be null;
   // [rows, n_heads * HD]) multiplies the output by its sigmoid. `split_p` carries the softmax's weights
   // into the second product as the sum of two bfloat16 numbers instead of one rounded one.
   int keep_first; int sink; const bf16* gate; int gate_row_stride; int split_p;

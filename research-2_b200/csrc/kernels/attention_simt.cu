@@ -55,7 +55,7 @@ attention_simt_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict__
   // With a window, the sequence's first `keep_first` keys stay visible: they are walked first, as a
   // range of their own, so that the walk depends on the row's position alone.
   const int kept = window > 0 ? (keep_first < first ? keep_first : first) : 0;
-  float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;   // a sink: one more score of 0 that has no value
+  float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;   // a sink: an extra exp(0) term in the sum, nothing in the output
   float acc[MAX_HEAD_DIM / 32];
 #pragma unroll
   for (int i = 0; i < MAX_HEAD_DIM / 32; ++i) acc[i] = 0.f;

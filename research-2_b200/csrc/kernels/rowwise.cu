@@ -221,7 +221,7 @@ template <typename T> __host__ __device__ inline bool pair_aligned(const T* p) {
 
 // ---------------------------------------------------------------------------------------------
 // RMS norm: y = x / sqrt(mean(x^2) + eps) * (offset + w), statistics in float. `offset` is 1 for a
-// weight that is stored around zero and 0 for a plain gain. `rows` (may be null) picks input rows.
+// weight tensor that holds the gain's offset from one and 0 for a plain gain. `rows` (may be null) picks input rows.
 // One warp per row, the row read twice (the second pass comes from L1/L2).
 template <typename O>
 __global__ void __launch_bounds__(128)
@@ -428,85 +428,75 @@ head_norm_pair_kernel(T* __restrict__ buf, int row_stride, int n_rows, int n_q_h
   }
 }
 
-// The same for head sizes up to 128 with eight heads of a row per warp: all their loads are issued before
-// the first sum, so that a launch of many rows is bound by bandwidth and not by one round trip per head.
-template <typename T>
+// bfloat16 with head sizes that are multiples of 8: a lane holds eight neighbouring elements (one 16-byte
+// access), a head lies in head_dim / 8 neighbouring lanes, and a warp takes as many whole heads of one row as
+// fit its 32 lanes. A head's sum of squares is gathered from its lanes by shuffles.
 __global__ void __launch_bounds__(128)
-head_norm_batch_kernel(T* __restrict__ buf, int row_stride, int n_rows, int n_q_heads, int n_k_heads, int head_dim,
-                       const float* __restrict__ w_q, const float* __restrict__ w_k, float eps, float offset,
-                       T* __restrict__ k_cache, T* __restrict__ v_cache, const int32_t* __restrict__ slot_mapping, int v_col,
-                       int v_head_dim, int page_size, long long page_stride, int n_pages) {
+head_norm_vec8_kernel(bf16* __restrict__ buf, int row_stride, int n_rows, int n_q_heads, int n_k_heads, int head_dim,
+                      const float* __restrict__ w_q, const float* __restrict__ w_k, float eps, float offset,
+                      bf16* __restrict__ k_cache, bf16* __restrict__ v_cache, const int32_t* __restrict__ slot_mapping, int v_col,
+                      int v_head_dim, int page_size, long long page_stride, int n_pages) {
   pdl_launch_dependents();
   pdl_wait();
-  constexpr int U = 8;
   const int lane = threadIdx.x & 31;
-  const int heads = n_q_heads + n_k_heads + (k_cache != nullptr ? n_k_heads : 0);
-  const int groups = (heads + U - 1) / U;
+  const int qk_heads = n_q_heads + n_k_heads;
+  const int lanes_qk = head_dim / 8, per_warp_qk = 32 / lanes_qk;            // lanes of a head; heads of a warp
+  const int slabs_qk = (qk_heads + per_warp_qk - 1) / per_warp_qk;
+  const int lanes_v = k_cache != nullptr ? v_head_dim / 8 : 1, per_warp_v = 32 / lanes_v;
+  const int slabs_v = k_cache != nullptr ? (n_k_heads + per_warp_v - 1) / per_warp_v : 0;
   const int w = blockIdx.x * 4 + (threadIdx.x >> 5);
-  if (w >= n_rows * groups) return;
-  const int r = w / groups, h0 = (w % groups) * U;
-  T* row = buf + size_t(r) * row_stride;
+  if (w >= n_rows * (slabs_qk + slabs_v)) return;
+  const int r = w / (slabs_qk + slabs_v), slab = w % (slabs_qk + slabs_v);
+  bf16* row = buf + size_t(r) * row_stride;
   size_t page_base = 0;
   int off = 0;
   bool cached = false;
-  if (k_cache != nullptr && h0 + U > n_q_heads) {
+  if (k_cache != nullptr) {
     const int slot = slot_mapping[r];
     const int page = slot / page_size;
     cached = slot >= 0 && page < n_pages;
     page_base = size_t(page) * page_stride;
     off = slot % page_size;
   }
-  // where head h0 + u begins in the row, and how long it is (a value head may have a size of its own)
-  float2 v[U][2];
-#pragma unroll
-  for (int u = 0; u < U; ++u) {
-    const int h = h0 + u;
-    const bool value = h >= n_q_heads + n_k_heads;
-    const int len = h < heads ? (value ? v_head_dim : head_dim) : 0;
-    const T* src = value ? row + v_col + size_t(h - n_q_heads - n_k_heads) * v_head_dim : row + size_t(h) * head_dim;
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int d = 2 * lane + 64 * i;
-      v[u][i] = d < len ? load2(src + d) : make_float2(0.f, 0.f);
+  if (slab >= slabs_qk) {  // value heads: copied as they are
+    const int vh = (slab - slabs_qk) * per_warp_v + lane / lanes_v, e = (lane % lanes_v) * 8;
+    if (cached && lane < per_warp_v * lanes_v && vh < n_k_heads) {
+      const uint4 x = *reinterpret_cast<const uint4*>(row + v_col + size_t(vh) * v_head_dim + e);
+      *reinterpret_cast<uint4*>(v_cache + page_base + (size_t(vh) * page_size + off) * v_head_dim + e) = x;
     }
+    return;
   }
-  float sq[U];
+  const int h = slab * per_warp_qk + lane / lanes_qk, e = (lane % lanes_qk) * 8;
+  const bool mine = lane < per_warp_qk * lanes_qk && h < qk_heads;
+  bf16* p = row + size_t(h) * head_dim + e;
+  uint4 x = make_uint4(0u, 0u, 0u, 0u);
+  if (mine) x = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&x);
+  float v[8];
+  float sq = 0.f;
 #pragma unroll
-  for (int u = 0; u < U; ++u) sq[u] = v[u][0].x * v[u][0].x + v[u][0].y * v[u][0].y + v[u][1].x * v[u][1].x + v[u][1].y * v[u][1].y;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-#pragma unroll
-    for (int u = 0; u < U; ++u) sq[u] += __shfl_xor_sync(0xffffffffu, sq[u], o);
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(x2[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+    sq += f.x * f.x + f.y * f.y;
   }
-#pragma unroll
-  for (int u = 0; u < U; ++u) {
-    const int h = h0 + u;
-    if (h >= heads) break;
-    if (h >= n_q_heads + n_k_heads) {  // a value head: copied as it is
-      if (cached) {
-        T* dst = v_cache + page_base + (size_t(h - n_q_heads - n_k_heads) * page_size + off) * v_head_dim;
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const int d = 2 * lane + 64 * i;
-          if (d < v_head_dim) store2(dst + d, v[u][i].x, v[u][i].y);
-        }
-      }
-      continue;
-    }
-    const float inv = 1.f / sqrtf(sq[u] / float(head_dim) + eps);
-    const float* gain = h < n_q_heads ? w_q : w_k;
-    T* p = row + size_t(h) * head_dim;
-    T* dst = (cached && h >= n_q_heads) ? k_cache + page_base + (size_t(h - n_q_heads) * page_size + off) * head_dim : nullptr;
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int d = 2 * lane + 64 * i;
-      if (d < head_dim) {
-        const float2 g = *reinterpret_cast<const float2*>(gain + d);
-        const T y0 = from_float<T>(v[u][i].x * inv * (offset + g.x)), y1 = from_float<T>(v[u][i].y * inv * (offset + g.y));
-        store2(p + d, to_float(y0), to_float(y1));
-        if (dst != nullptr) store2(dst + d, to_float(y0), to_float(y1));
-      }
-    }
+  float total = 0.f;
+  const int first_lane = (lane / lanes_qk) * lanes_qk;
+  for (int j = 0; j < lanes_qk; ++j) total += __shfl_sync(0xffffffffu, sq, (first_lane + j) & 31);
+  if (!mine) return;
+  const float inv = 1.f / sqrtf(total / float(head_dim) + eps);
+  const float* gain = (h < n_q_heads ? w_q : w_k) + e;
+  const float4 g0 = *reinterpret_cast<const float4*>(gain), g1 = *reinterpret_cast<const float4*>(gain + 4);
+  uint4 y;
+  __nv_bfloat162* y2 = reinterpret_cast<__nv_bfloat162*>(&y);
+  y2[0] = __floats2bfloat162_rn(v[0] * inv * (offset + g0.x), v[1] * inv * (offset + g0.y));
+  y2[1] = __floats2bfloat162_rn(v[2] * inv * (offset + g0.z), v[3] * inv * (offset + g0.w));
+  y2[2] = __floats2bfloat162_rn(v[4] * inv * (offset + g1.x), v[5] * inv * (offset + g1.y));
+  y2[3] = __floats2bfloat162_rn(v[6] * inv * (offset + g1.z), v[7] * inv * (offset + g1.w));
+  *reinterpret_cast<uint4*>(p) = y;
+  if (cached && h >= n_q_heads) {
+    *reinterpret_cast<uint4*>(k_cache + page_base + (size_t(h - n_q_heads) * page_size + off) * head_dim + e) = y;
   }
 }
 
@@ -524,20 +514,19 @@ extern "C" int r2_head_norm(void* buf, int row_stride, int n_rows, int n_q_heads
   const bool pairs = head_dim % 2 == 0 && head_dim <= 512 && row_stride % 2 == 0 && even(buf) && even(w_q) && even(w_k) &&
                      !(reinterpret_cast<uintptr_t>(w_q) & 7) && !(reinterpret_cast<uintptr_t>(w_k) & 7) &&
                      (k_cache == nullptr || (v_col % 2 == 0 && v_head_dim % 2 == 0 && page_stride % 2 == 0 && even(k_cache) && even(v_cache)));
-  if (pairs && head_dim <= 128 && (k_cache == nullptr || v_head_dim <= 128)) {
-    const int heads = n_q_heads + n_k_heads + (k_cache != nullptr ? n_k_heads : 0);
-    const long long warps = (long long)n_rows * ((heads + 7) / 8);
-    dim3 bgrid((unsigned)((warps + 3) / 4));
-    if (dtype == R2_F32) {
-      r2_launch(head_norm_batch_kernel<float>, bgrid, dim3(128), size_t(0), stream, (float*)buf, row_stride, n_rows, n_q_heads, n_k_heads, head_dim, w_q, w_k, eps, offset,
-                (float*)k_cache, (float*)v_cache, slot_mapping, v_col, v_head_dim, page_size, page_stride, n_pages);
-      return launch_status();
+  auto on16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  if (dtype == R2_BF16 && head_dim % 8 == 0 && head_dim <= 256 && row_stride % 8 == 0 && on16(buf) && on16(w_q) && on16(w_k) &&
+      (k_cache == nullptr || (v_head_dim % 8 == 0 && v_head_dim <= 256 && v_col % 8 == 0 && page_stride % 8 == 0 && on16(k_cache) && on16(v_cache)))) {
+    const int per_warp_qk = 32 / (head_dim / 8);
+    int slabs = (n_q_heads + n_k_heads + per_warp_qk - 1) / per_warp_qk;
+    if (k_cache != nullptr) {
+      const int per_warp_v = 32 / (v_head_dim / 8);
+      slabs += (n_k_heads + per_warp_v - 1) / per_warp_v;
     }
-    if (dtype == R2_BF16) {
-      r2_launch(head_norm_batch_kernel<bf16>, bgrid, dim3(128), size_t(0), stream, (bf16*)buf, row_stride, n_rows, n_q_heads, n_k_heads, head_dim, w_q, w_k, eps, offset,
-                (bf16*)k_cache, (bf16*)v_cache, slot_mapping, v_col, v_head_dim, page_size, page_stride, n_pages);
-      return launch_status();
-    }
+    const long long warps = (long long)n_rows * slabs;
+    r2_launch(head_norm_vec8_kernel, dim3((unsigned)((warps + 3) / 4)), dim3(128), size_t(0), stream, (bf16*)buf, row_stride, n_rows, n_q_heads, n_k_heads,
+              head_dim, w_q, w_k, eps, offset, (bf16*)k_cache, (bf16*)v_cache, slot_mapping, v_col, v_head_dim, page_size, page_stride, n_pages);
+    return launch_status();
   }
   if (pairs && dtype == R2_F32) {
     r2_launch(head_norm_pair_kernel<float>, grid, dim3(128), size_t(0), stream, (float*)buf, row_stride, n_rows, n_q_heads, n_k_heads, head_dim, w_q, w_k, eps, offset,

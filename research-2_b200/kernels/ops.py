@@ -408,7 +408,7 @@ def layer_norm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: fl
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype, rows: torch.Tensor | None = None,
              unit_offset: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:
     """x / sqrt(mean(x^2) + eps) * w of float32 rows, statistics in float32; with `unit_offset` the gain is
-    1 + w (a weight stored around zero). `rows` (int32) picks input rows, else all rows in order."""
+    1 + w (the tensor holds the gain's offset from one). `rows` (int32) picks input rows, else all rows in order."""
     _need(x, "x", torch.float32, 2)
     _need(weight, "weight", torch.float32, 1)
     if not x.is_contiguous() or weight.shape[0] != x.shape[1]:
@@ -651,7 +651,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                     keep_first: int = 0, sink: bool = False, gate: torch.Tensor | None = None) -> torch.Tensor:
     """Causal attention of q [T, n_heads * head_dim] over the paged cache -> [T, n_heads * v_head_dim]
     (`v_head_dim` 0: the keys' head size). With a window, `keep_first` keeps a sequence's first keys visible;
-    `sink` adds one to the softmax's denominator (a key of score 0 that has no value); `gate`
+    `sink` adds one to the softmax's denominator (an extra exp(0) term: the weights sum to less than one); `gate`
     [T, n_heads * v_head_dim] multiplies the output by its sigmoid.
     `decode_only` says that every row is an entry of its own (one new token each) and
     `max_context` bounds the rows' context lengths; `q_start` (int32 [R + 1]) with `n_tiles`, the

@@ -1,7 +1,7 @@
 """Zirunex as data: its tensor names, its random initialisation, and its ModelSpec.
 
 A decoder of parallel blocks, x + mixer(h) + feed_forward(h) with h = rms_norm(x), whose norms' weights
-are stored around zero (gain 1 + w). The token table's rows are scaled on their way in; the head is a
+hold the gain's offset from one (gain 1 + w). The token table's rows are scaled on their way in; the head is a
 table of its own. A layer's mixer is grouped attention with query/key norms, a window that keeps the
 first tokens, a sink and an output gate (parts/attention.py: `qk_norm_attention`); its feed-forward, where
 it has one, is the gated form with clamped projections (parts/mlp.py: `gated_clamped`). A layer may run
@@ -56,7 +56,7 @@ def weight_spec(cfg: ZirunexConfig) -> WeightSpec:
 
 def random_weights(cfg: ZirunexConfig, seed: int, std: float = 0.05, norm_std: float = 0.1) -> dict[str, torch.Tensor]:
     """Float32 draws from ONE CPU generator, in the order of `weight_spec`: matrices and tables N(0, std),
-    norm weights N(0, norm_std) (they are stored around zero), query/key gains 1 + N(0, norm_std)."""
+    norm weights N(0, norm_std) (offsets from a gain of one), query/key gains 1 + N(0, norm_std)."""
     gen = torch.Generator(device="cpu")
     gen.manual_seed(seed)
     out: dict[str, torch.Tensor] = {}

@@ -104,7 +104,7 @@ class QKNormAttention:
     params: n_heads, n_kv_heads, head_dim, v_head_dim, scale, qk_norm_eps, qk_norm_unit_offset (false: the
     norms' weights are plain gains), window (0 = none; a row at position p reads the keys (p - window, p]),
     keep_first (with a window: keys at positions below it stay visible), sink (the softmax's denominator is
-    1 + the sum, i.e. one more key of score 0 that has no value).
+    1 + the sum of the exponentials: an extra exp(0) term, so the weights sum to less than one).
     weights, all matrices stored [out, in] and without biases: w_q [H * head_dim, D], w_k [G * head_dim, D],
     w_v [G * v_head_dim, D], w_out [D, H * v_head_dim], q_norm [head_dim], k_norm [head_dim], and optionally
     w_gate [H * v_head_dim, D]: the heads' outputs are multiplied by sigmoid(w_gate h) before w_out.

@@ -33,8 +33,8 @@ class LayerNorm:
 
 @register_norm("rms_norm")
 class RMSNorm:
-    """x / sqrt(mean(x^2) + eps) * gain. params: eps; unit_offset (the stored weight lies around zero and the
-    gain is 1 + weight; default false: the weight is the gain). weights: weight."""
+    """x / sqrt(mean(x^2) + eps) * gain. params: eps; unit_offset (the stored weight is the gain's offset from one:
+    gain = 1 + weight; default false: the weight is the gain). weights: weight."""
 
     can_be_lazy = True
 

@@ -32,12 +32,12 @@ def embed(tokens: torch.Tensor, table: torch.Tensor, scale: float) -> torch.Tens
 
 
 def rms(x: torch.Tensor, eps: float) -> torch.Tensor:
-    """x over its root mean square along the last axis, eps inside the root."""
+    """x over sqrt(mean(x^2) + eps) along the last axis."""
     return x / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + eps)
 
 
 def stream_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
-    """The norm of the residual stream: the stored weight lies around zero, the gain is 1 + w."""
+    """The norm of the residual stream: the tensor w holds the gain's offset from one: gain 1 + w."""
     return rms(x, eps) * (1.0 + w)
 
 

@@ -70,6 +70,52 @@ def test_stream_norm_and_head_norm(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("sizes", [(5, 2, 48, 16, 8), (4, 4, 64, 64, 16), (3, 1, 24, 40, 4), (2, 1, 256, 128, 2)])
+def test_head_norm_that_writes_the_cache(dtype, sizes):
+    """The launch that norms the query and key heads also puts the normed keys and the values into the rows'
+    slots: the cache then holds exactly what the projection's key columns hold, and the value columns."""
+    from research_2_b200.cache.arena import KVArena, MemberSpec, derive_groups
+    from research_2_b200.kernels import ops
+
+    n_q, n_k, d, vd, page = sizes
+    rows, extra = 37, 24
+    gen = torch.Generator().manual_seed(3)
+    width = (n_q + n_k) * d + n_k * vd + extra
+    buf = (torch.randn(rows, width, generator=gen) * 2.0).to(dtype)
+    gq, gk = torch.rand(d, generator=gen) + 0.5, torch.rand(d, generator=gen) + 0.5
+    member = MemberSpec(n_k, d, 0, vd, 0)
+    groups, index = derive_groups([member], page, 40)
+    arena = KVArena([member], groups, index, dtype, DEV)
+    arena.fill_(9.0)
+    cache = arena.members[0]
+    slots = (torch.randperm(40 * page, generator=gen)[:rows] + page).to(torch.int32)
+    dev = buf.to(DEV)
+    slots_dev = slots.to(DEV)   # (the scatter description holds its address only)
+    scatter = ops.kv_scatter(slots_dev, cache.k, cache.v, cache.page_stride, page, cache.n_pages, (n_q + n_k) * d, n_k * vd, vd)
+    ops.head_norm(dev, n_q, n_k, d, gq.to(DEV), gk.to(DEV), 1e-6, kv=scatter)
+    got = dev.cpu()
+    heads = buf.double()[:, : (n_q + n_k) * d].view(rows, n_q + n_k, d)
+    want_q = plain.head_norm(heads[:, :n_q], gq.double(), 1e-6).reshape(rows, -1)
+    want_k = plain.head_norm(heads[:, n_q:], gk.double(), 1e-6).reshape(rows, -1)
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert torch.allclose(got[:, : n_q * d].double(), want_q, atol=tol * float(want_q.abs().max()), rtol=0)
+    assert torch.allclose(got[:, n_q * d: (n_q + n_k) * d].double(), want_k, atol=tol * float(want_k.abs().max()), rtol=0)
+    assert torch.equal(got[:, (n_q + n_k) * d:], buf[:, (n_q + n_k) * d:]), "values and what follows are left alone"
+    pool = arena.tensors[0].cpu()
+    k_elems = n_k * page * d
+    for r in range(rows):
+        pg, off = int(slots[r]) // page, int(slots[r]) % page
+        k_page = pool[pg, :k_elems].view(n_k, page, d)
+        v_page = pool[pg, k_elems: k_elems + n_k * page * vd].view(n_k, page, vd)
+        assert torch.equal(k_page[:, off], got[r, n_q * d: (n_q + n_k) * d].view(n_k, d)), r
+        assert torch.equal(v_page[:, off], buf[r, (n_q + n_k) * d: (n_q + n_k) * d + n_k * vd].view(n_k, vd)), r
+    written = torch.zeros(41, page, dtype=torch.bool)
+    written[slots.long() // page, slots.long() % page] = True
+    untouched = pool[:, :k_elems].view(41, n_k, page, d)[~written[:, None, :].expand(41, n_k, page)]
+    assert bool((untouched == 9.0).all()), "a slot of no row was written"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_gated_unit_and_scaled_embedding(dtype):
     from research_2_b200.kernels import ops
 
