@@ -59,6 +59,12 @@ struct Params {
   float scale; int window;
   int box_rows;
   int* error_flag;
+  // The form with extras (template parameter X). With a window, an entry's first `keep_first` keys stay
+  // visible beside the window's. `sink` adds one to every softmax's denominator (an extra exp(0) term).
+  // `gate` (may be null; [rows, n_heads * 64]) multiplies the output by its sigmoid. `split_p` hands the
+  // softmax's weights to the second product as the sum of two bfloat16 terms: the second term lies in the
+  // other half of the score buffer that the thread has read, and the product is issued once per term.
+  int keep_first; int sink; const bf16* gate; int gate_row_stride; int split_p;
 };
 
 using namespace r2ptx;
@@ -67,7 +73,7 @@ using namespace r2ptx;
 // accesses are consecutive.
 constexpr int JOIN_BYTES = (HD + 2) * BM * 4;
 
-template <int SPLIT>
+template <int SPLIT, bool X>
 __global__ void __launch_bounds__(THREADS)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                   const __grid_constant__ CUtensorMap map_v, const Params p) {
@@ -184,7 +190,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   const int lo = p.window > 0 ? max(0, pmin - p.window + 1) : 0;
   const int32_t* table = p.block_tables + size_t(e) * p.table_width;
   const int j_first = lo / BN * BN;
-  const int n_tiles = (pmax - j_first) / BN + 1;
+  // (X) the key tiles of the rows: first those that hold kept first keys below the window's first tile, then
+  // the window's
+  const int keep = (X && p.window > 0) ? p.keep_first : 0;
+  const int n_kept_tiles = X ? (min(keep, j_first) + BN - 1) / BN : 0;
+  const int n_tiles = n_kept_tiles + (pmax - j_first) / BN + 1;
   // Rows with few keys stay with the first CTA of the two: the second would cost more than it saves.
   const bool joined = SPLIT > 1 && n_tiles >= 4;
   if (SPLIT > 1 && !joined && chain != 0) {
@@ -194,7 +204,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
   // This CTA's tiles: number i of them is tile step * i + chain of the rows, keys from j_of(i) on.
   const int step = joined ? SPLIT : 1;
   const int n_mine = (n_tiles - chain + step - 1) / step;
-  auto j_of = [&](int i) { return j_first + (step * i + chain) * BN; };
+  auto j_of = [&](int i) {
+    const int t = step * i + chain;
+    return (X && t < n_kept_tiles) ? t * BN : j_first + (t - n_kept_tiles) * BN;
+  };
 
   // (a softmax thread's running maximum and sum, and whether its waits all came true: they outlive the role's block)
   float m_run = -INFINITY, l_run = 0.f;
@@ -210,7 +223,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       box_page = INT_MIN;
       if (lane < n_boxes) {
         const int jb = j0 + lane * p.box_rows;
-        if (jb + p.box_rows - 1 >= lo && jb <= pmax) box_page = table[page_index(jb, p.page_size, p.page_shift)];
+        if ((jb + p.box_rows - 1 >= lo || jb < keep) && jb <= pmax) box_page = table[page_index(jb, p.page_size, p.page_shift)];
       }
     };
     if (n_mine > 0) box_lookup(j_of(0));
@@ -298,6 +311,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
           umma_bf16_a_tmem(tmem_o, tmem_base + uint32_t(it & 1) * 64u + uint32_t(kk * 8), mnmajor + uint64_t(vt + kk * 128), idesc_o,
                            (it > 0 || kk > 0) ? 1u : 0u);
         }
+        if (X && p.split_p) {  // the weights' second terms: columns [32, 64) of the same score buffer
+#pragma unroll
+          for (int kk = 0; kk < BN / 16; ++kk) {
+            umma_bf16_a_tmem(tmem_o, tmem_base + uint32_t(it & 1) * 64u + 32u + uint32_t(kk * 8), mnmajor + uint64_t(vt + kk * 128), idesc_o, 1u);
+          }
+        }
         umma_commit(kv_empty_a + uint32_t(stage) * 8u);
         umma_commit(pv_done_a);
         if (it == n_mine - 1) umma_commit(o_done_a);
@@ -340,11 +359,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       // logic on two registers: written with && and || over the position this loop took 1,300 cycles a tile).
       const int hi = pos - j0;
       const int lo_c = p.window > 0 ? pos - p.window + 1 - j0 : 0;
-      if (hi < BN - 1 || lo_c > 0) {
+      const int kf = keep - j0;   // (X) keys of the tile below it are kept first keys; without them it is <= 0
+      if (hi < BN - 1 || (lo_c > 0 && kf < BN)) {
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
-          const bool seen_a = (c <= hi) & (c >= lo_c);
-          const bool seen_b = (c + 32 <= hi) & (c + 32 >= lo_c);
+          const bool seen_a = (c <= hi) & ((c >= lo_c) | (X && c < kf));
+          const bool seen_b = (c + 32 <= hi) & ((c + 32 >= lo_c) | (X && c + 32 < kf));
           s0[c] = seen_a ? s0[c] : __float_as_uint(-INFINITY);
           s1[c] = seen_b ? s1[c] : __float_as_uint(-INFINITY);
         }
@@ -361,6 +381,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       const float corr = grow ? fast_exp2(m_run - base) : 1.f;
       float sum_a = 0.f, sum_b = 0.f;
       uint32_t pk[32];  // the row of P, two bfloat16 to a word: keys 2w and 2w + 1
+      uint32_t pr[X ? 32 : 1];  // (X) what the rounding left of each weight, as a second row of bfloat16
 #pragma unroll
       for (int w = 0; w < 16; ++w) {
         const float a0 = fast_exp2(fmaf(__uint_as_float(s0[2 * w]), scale2, -base));
@@ -371,6 +392,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         sum_b += b0 + b1;
         pk[w] = pack_bf16(a0, a1);
         pk[16 + w] = pack_bf16(b0, b1);
+        if (X) {
+          const float2 ha = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pk[w]));
+          const float2 hb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pk[16 + w]));
+          pr[w] = pack_bf16(a0 - ha.x, a1 - ha.y);
+          pr[16 + w] = pack_bf16(b0 - hb.x, b1 - hb.y);
+        }
       }
       l_run = l_run * corr + (sum_a + sum_b);
       m_run = m_new;
@@ -393,13 +420,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
         }
       }
       tmem_store32(s_at, pk);  // over the scores this thread has read
+      if constexpr (X) {
+        if (p.split_p) tmem_store32(s_at + 32u, pr);   // the other half of the same buffer, which this thread has read too
+      }
       fetch(it + 1);           // (the registers of the scores are free)
-      if (j0 < lo || j0 + BN - 1 > pmax) {
+      if ((j0 < lo && j0 + BN > keep) || j0 + BN - 1 > pmax) {
         // Keys of this tile outside those that any row may see were not copied, or hold whatever
         // their slots held: their p is 0, but the product multiplies, so their value rows must
         // be finite. They are set to zero (the stage has landed: its scores exist).
         const int j = j0 + row;
-        if (row < BN && (j < lo || j > pmax)) {
+        if (row < BN && ((j < lo && j >= keep) || j > pmax)) {
           const uint32_t dst = smem_u32(v_s) + uint32_t((it % STAGES) * KV_BYTES + row * 128);
 #pragma unroll
           for (int c = 0; c < 8; ++c) asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(dst + c * 16), "r"(0u) : "memory");
@@ -452,14 +482,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
     const int q = warp & 3, row = q * 32 + lane;
     const uint32_t lane_base = tmem_base + (uint32_t(q * 32) << 16);
     float w_mine = 1.f, w_other = 0.f, l_all = l_run;
+    float m_all = m_run;   // the maximum (in units of log2 e) that l_all stands against
     if (joined) {
       const float m_other = join_s[HD * BM + row], l_other = join_s[(HD + 1) * BM + row];
-      const float m_all = fmaxf(m_run, m_other);
+      m_all = fmaxf(m_run, m_other);
       const float base = m_all == -INFINITY ? 0.f : m_all;
       w_mine = fast_exp2(m_run - base);
       w_other = fast_exp2(m_other - base);
       l_all = l_run * w_mine + l_other * w_other;
     }
+    if (X && p.sink) l_all += m_all > -INFINITY ? fast_exp2(-m_all) : 1.f;   // one more term exp(0) in the denominator
     const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
     w_mine *= inv;
     w_other *= inv;
@@ -476,6 +508,22 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_consta
       for (int c = 0; c < 32; ++c) {
         r[c] = __uint_as_float(o[c]) * w_mine;
         if (joined) r[c] = fmaf(join_s[(part * 32 + c) * BM + row], w_other, r[c]);
+      }
+      if constexpr (X) {
+        if (p.gate != nullptr) {  // times the sigmoid of the row's gate values (a row past the entry's last reads the last one's)
+          const bf16* g = p.gate + size_t(t0 + r0 + min(row, rows_here - 1)) * p.gate_row_stride + size_t(h) * HD + part * 32;
+#pragma unroll
+          for (int c8 = 0; c8 < 4; ++c8) {
+            const uint4 gv = *reinterpret_cast<const uint4*>(g + c8 * 8);
+            const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 f = __bfloat1622float2(g2[i]);
+              r[c8 * 8 + 2 * i] *= 1.f / (1.f + __expf(-f.x));
+              r[c8 * 8 + 2 * i + 1] *= 1.f / (1.f + __expf(-f.y));
+            }
+          }
+        }
       }
 #pragma unroll
       for (int c8 = 0; c8 < 4; ++c8) {
@@ -530,9 +578,11 @@ extern "C" int r2_attention_prefill_tc(const void* q, int q_row_stride, int n_ro
                                        const void* v_cache, long long page_stride, int page_size, int n_pages,
                                        const int32_t* block_tables, int table_width, const int32_t* q_start,
                                        const int32_t* seq_lens, int n_entries, int n_tiles, int n_heads, int n_kv_heads,
-                                       float scale, int window, int* error_flag, cudaStream_t stream) {
+                                       float scale, int window, int* error_flag, int keep_first, int sink, const void* gate,
+                                       int gate_row_stride, int split_p, cudaStream_t stream) {
   if (n_entries <= 0 || n_tiles <= 0 || n_rows <= 0) return R2_OK;
-  if (n_heads < 1 || n_kv_heads < 1 || n_heads % n_kv_heads != 0 || page_size < 1 || window < 0) return R2_BAD_SHAPE;
+  if (n_heads < 1 || n_kv_heads < 1 || n_heads % n_kv_heads != 0 || page_size < 1 || window < 0 || keep_first < 0) return R2_BAD_SHAPE;
+  if (gate != nullptr && (gate_row_stride % 8 != 0 || (reinterpret_cast<uintptr_t>(gate) & 15))) return R2_UNSUPPORTED;
   const bool page_fits = page_size == 8 || page_size == 16 || page_size == 32 || page_size % 64 == 0;
   if (!page_fits || error_flag == nullptr || !(scale > 0.f)) return R2_UNSUPPORTED;
   if (page_stride % 8 != 0 || q_row_stride % 8 != 0 || out_row_stride % 8 != 0 || (reinterpret_cast<uintptr_t>(k_cache) & 15) ||
@@ -548,6 +598,8 @@ extern "C" int r2_attention_prefill_tc(const void* q, int q_row_stride, int n_ro
   p.scale = scale; p.window = window;
   p.box_rows = page_size < 64 ? page_size : 64;
   p.error_flag = error_flag;
+  p.keep_first = keep_first; p.sink = sink; p.gate = (const bf16*)gate; p.gate_row_stride = gate_row_stride; p.split_p = split_p;
+  const bool extras = keep_first > 0 || sink != 0 || gate != nullptr || split_p != 0;
   CUtensorMap mq, mk, mv;
   if (!query_map(&mq, q, n_rows, q_row_stride, n_heads) ||
       !r2::page_map(&mk, k_cache, page_stride, page_size, n_kv_heads, n_pages, p.box_rows, HD) ||
@@ -561,10 +613,14 @@ extern "C" int r2_attention_prefill_tc(const void* q, int q_row_stride, int n_ro
   if (!configured) {
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) return R2_UNSUPPORTED;
-    cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 120 * 1024);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_two));
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_tc_kernel<1>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_tc_kernel<2>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 120 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_tc_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_two));
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_tc_kernel<1, false>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_tc_kernel<2, false>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_tc_kernel<1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 120 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_tc_kernel<2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem_two));
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_tc_kernel<1, true>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(prefill_tc_kernel<2, true>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
     if (e != cudaSuccess) return int(e);
     configured = true;
   }
@@ -588,14 +644,16 @@ extern "C" int r2_attention_prefill_tc(const void* q, int q_row_stride, int n_ro
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     config.attrs = attr;
     config.numAttrs = (g_r2_pdl && !t_r2_plain_order) ? 2 : 1;
-    cudaLaunchKernelEx(&config, prefill_tc_kernel<2>, mq, mk, mv, p);  // a failure shows in launch_status()
+    if (extras) cudaLaunchKernelEx(&config, prefill_tc_kernel<2, true>, mq, mk, mv, p);  // a failure shows in launch_status()
+    else cudaLaunchKernelEx(&config, prefill_tc_kernel<2, false>, mq, mk, mv, p);
   } else {
     // Two CTAs share an SM's special-function units and each runs slower for it. With many CTAs that is the
     // better trade (one CTA's softmax under the other's products); with fewer than two per SM the step waits
     // for the CTA with the most keys, which then should have an SM to itself: the CTA asks for more than half
     // an SM's shared memory, and the ones that do not fit at first start as the short ones end.
     const size_t smem = busy <= 2L * n_sms ? size_t(120) * 1024 : smem_one;
-    r2_launch(prefill_tc_kernel<1>, dim3(n_heads, n_tiles), dim3(THREADS), smem, stream, mq, mk, mv, p);
+    if (extras) r2_launch(prefill_tc_kernel<1, true>, dim3(n_heads, n_tiles), dim3(THREADS), smem, stream, mq, mk, mv, p);
+    else r2_launch(prefill_tc_kernel<1, false>, dim3(n_heads, n_tiles), dim3(THREADS), smem, stream, mq, mk, mv, p);
   }
   return launch_status();
 }

@@ -197,6 +197,17 @@ def use_prefill_tc(on):
     return before
 
 
+_prefill_tc_extras = os.environ.get("R2_PREFILL_TC_EXTRAS", "1") != "0"
+
+
+def use_prefill_tc_extras(on: bool) -> bool:
+    """Whether attention with kept first keys, a sink or a gate may run on the tcgen05 prefill kernel (head
+    size 64); off, it runs on the mma.sync kernel (tests compare the two). Returns the previous setting."""
+    global _prefill_tc_extras
+    before, _prefill_tc_extras = _prefill_tc_extras, bool(on)
+    return before
+
+
 def use_prefill_tma(on: bool, head_dim: int = 64) -> bool:
     """Switch how the prefill attention kernel brings key and value tiles in: 4-D tensor copies
     (TMA, one per page; head size 64 and page sizes 8, 16, 32 or multiples of 64) or 16-byte
@@ -679,7 +690,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         gate_stride = _rows(gate, "gate")
     group = n_heads // max(n_kv_heads, 1)
     # only the general kernel takes a value head size of its own or a head size that is no multiple of 16; kept
-    # first keys, a sink and an output gate are taken by the mma.sync prefill kernel and the fused decode kernel
+    # first keys, a sink and an output gate are taken by both prefill kernels and the fused decode kernel
     fits = v_head_dim == head_dim and head_dim % 16 == 0
     plain = fits and keep_first == 0 and not sink and gate is None
     if plain and q.dtype == torch.bfloat16 and decode_only and _fast_attention and group in (1, 2, 4, 8):
@@ -698,7 +709,8 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         if n_slices > 1:
             count_launches(1)  # the merge kernel
         return out
-    if plain and q.dtype == torch.bfloat16 and _fast_attention and _prefill_tc and q_start is not None and n_tiles > 0 and head_dim == 64:
+    if (fits and q.dtype == torch.bfloat16 and _fast_attention and _prefill_tc and q_start is not None and n_tiles > 0 and head_dim == 64
+            and (plain or _prefill_tc_extras)):
         # tcgen05 form (head size 64, pages of 8, 16, 32 or a multiple of 64 keys): 128-row tiles, one entry to a
         # tile. Also where most tiles are mostly empty (single decoded tokens beside a portion: 64 such rows
         # and 448 of a prompt take 40 us against the mma.sync kernel's 49).
@@ -707,7 +719,8 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         status = _lib("attention_prefill_tc").r2_attention_prefill_tc(
             _p(q), _rows(q, "q"), n, _p(out), _rows(out, "out"), _p(k_cache), _p(v_cache), C.c_longlong(page_stride),
             page_size, n_pages, _p(block_tables), block_tables.shape[1], _p(q_start), _p(seq_lens), n_entries,
-            (n_tiles + n_entries + 1) // 2, n_heads, n_kv_heads, C.c_float(scale), window, _p(_workspace(q.device).error), _stream())
+            (n_tiles + n_entries + 1) // 2, n_heads, n_kv_heads, C.c_float(scale), window, _p(_workspace(q.device).error),
+            keep_first, int(bool(sink)), _p(gate), gate_stride, int(_exact_weights and not plain), _stream())
         if status != -4:
             _check(status, "paged_attention (prefill, tcgen05)")
             _used("attention_prefill_tc")

@@ -69,9 +69,9 @@ class ParallelBlock:
 
     def forward(self, x, ctx, cache=None, state=None, writes_cache: bool = True):
         if self.w_in is not None:
-            # (the norm stays a kernel of its own: inside the joint product's kernel, where every CTA of a product
-            # several thousand columns wide normalises the rows again, a decode step of 8 rows measured 0.48 ms
-            # against 0.39)
+            # (the norm stays a kernel of its own: computed inside the joint product's kernel, where every CTA of a
+            # product several thousand columns wide normalises the rows again, a decode step of 8 rows and 12
+            # layers measured 0.48 ms against 0.40)
             h = self.norm_1.forward(x, self.compute_dtype)
             proj = ops.linear(h, self.w_in, None, w_is_nk=True)
             x = self.mixer.forward_projected(proj[:, : self.split], x, ctx, cache, state, writes_cache)

@@ -224,9 +224,15 @@ def gated_cases(rows: int = 8, kv_heads: int | None = None, window: int = 256, k
 
         flops = sum(4 * Q * pairs(r, length) for r, length in entries)
         what = "every key" if win == 0 else f"window {win} + {keep} kept"
-        out.append((f"prefill gated sink attention on mma.sync, {name} x {H} heads ({G} kv), {what}",
-                    lambda: ops.paged_attention(q, kc, vc, page_stride, PS, n_pages, tables, row_entry, positions, lens, H, G, HD, HD**-0.5,
-                                                win, q_start=q_start, n_tiles=n_tiles, keep_first=keep, sink=True, gate=gate), 0, flops))
+        def attention(tc):
+            before = ops.use_prefill_tc_extras(tc)
+            ops.paged_attention(q, kc, vc, page_stride, PS, n_pages, tables, row_entry, positions, lens, H, G, HD, HD**-0.5,
+                                win, q_start=q_start, n_tiles=n_tiles, keep_first=keep, sink=True, gate=gate)
+            ops.use_prefill_tc_extras(before)
+
+        if HD == 64:
+            out.append((f"prefill gated sink attention on tcgen05, {name} x {H} heads ({G} kv), {what}", lambda: attention(True), 0, flops))
+        out.append((f"prefill gated sink attention on mma.sync, {name} x {H} heads ({G} kv), {what}", lambda: attention(False), 0, flops))
 
     for win, keep in ((0, 0), (window, keep_first)):
         attention_case("2 x 1,024 tokens", [(1024, 1024)] * 2, win, keep)

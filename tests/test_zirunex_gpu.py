@@ -219,6 +219,8 @@ ATTENTION_SHAPES = [
     (2, 2, 16, 16, 5, 0, 8),
     (3, 1, 24, 40, 9, 12, 4),      # only the general kernel takes it
     (2, 1, 128, 128, 130, 3, 16),
+    (6, 2, 32, 32, 20, 2, 8),      # three query heads a kv head: decoded rows go through the prefill kernel
+    (5, 5, 48, 48, 33, 1, 16),
 ]
 
 
@@ -237,12 +239,13 @@ def test_attention_prompts_portions_and_decoded_rows(dtype, shape):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("decode", [False, True])
-def test_one_key_that_stands_out_at_every_edge(dtype, decode):
+@pytest.mark.parametrize("dim", [32, 64])
+def test_one_key_that_stands_out_at_every_edge(dtype, decode, dim):
     """One key whose score dwarfs all others and whose value is 40: at the last place inside the window
     the row's first head returns (nearly) that value, one place further out it returns an ordinary
     mixture; the same at the last kept first token and the first one that is not kept; for rows in a
     prompt's portion and for decoded rows, with the key far behind a page's border."""
-    heads, kv, dim, window, keep, page = 2, 1, 32, 40, 6, 16
+    heads, kv, window, keep, page = 2, 1, 40, 6, 16   # (head size 64 in bfloat16: the tcgen05 kernel)
     n = 230
     for row_pos, distance, seen in (
         (n - 1, window - 1, True), (n - 1, window, False),              # the window's far edge
@@ -264,6 +267,31 @@ def test_one_key_that_stands_out_at_every_edge(dtype, decode):
         # the plain implementation itself shows the planted key exactly where the mask says
         assert (float(b[:dim].abs().max()) > 5.0) == seen, (row_pos, distance, float(b[:dim].abs().max()))
         assert (float(a[:dim].abs().max()) > 5.0) == seen, (row_pos, distance, decode, float(a[:dim].abs().max()))
+
+
+@pytest.mark.parametrize("page", [8, 16, 32, 64])
+def test_head_size_64_on_both_prefill_kernels(page):
+    """Head size 64 runs on the tcgen05 kernel (two-term weights in the two halves of a score buffer, kept
+    tiles before the window's, sink, gate) and, switched off, on the mma.sync kernel: both against the plain
+    implementation, with one prompt (CTA pairs share the keys), several, and decoded rows beside portions."""
+    from research_2_b200.kernels import ops
+
+    for tc in (True, False):
+        before_setting = ops.use_prefill_tc_extras(tc)
+        before = ops.kernel_uses()
+        try:
+            for shape in ((4, 2, 64, 64, 100, 70, page), (8, 1, 64, 64, 70, 5, page), (2, 2, 64, 64, 1000, 0, page)):
+                for lengths, new_rows in (((700,), (700,)), ((150, 37, 401, 64, 9), (150, 2, 277, 1, 9)), ((520, 300), (200, 129))):
+                    out, want = _attention_case(torch.bfloat16, *shape, lengths, new_rows, seed=5)
+                    for e, (a, b) in enumerate(zip(out, want)):
+                        err = (a - b).abs().max(dim=1).values
+                        assert float(err.max()) <= 2e-2 * max(1.0, float(b.abs().max())), (tc, shape, lengths, e, int(err.argmax()), float(err.max()))
+        finally:
+            ops.use_prefill_tc_extras(before_setting)
+        after = ops.kernel_uses()
+        name = "attention_prefill_tc" if tc else "attention_prefill"
+        assert after.get(name, 0) - before.get(name, 0) == 9, (tc, before, after)
+    assert ops.device_errors(DEV) == 0
 
 
 def test_the_fast_kernels_are_the_ones_that_run():
