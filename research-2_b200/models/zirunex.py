@@ -82,7 +82,7 @@ def model_spec(cfg: ZirunexConfig) -> ModelSpec:
         mixer = PartSpec(
             "qk_norm_attention",
             {"n_heads": m.heads, "n_kv_heads": m.kv_heads, "head_dim": m.dim, "v_head_dim": m.vdim, "scale": m.scale,
-             "window": m.window, "keep_first": m.keep_first, "sink": True, "qk_norm_eps": cfg.norm_eps,
+             "window": min(m.window, UNBOUNDED_SEQ_LEN), "keep_first": min(m.keep_first, UNBOUNDED_SEQ_LEN), "sink": True, "qk_norm_eps": cfg.norm_eps,
              "qk_norm_unit_offset": False},
             {"w_q": f"{p}.mix.q", "w_k": f"{p}.mix.k", "w_v": f"{p}.mix.v", "w_gate": f"{p}.mix.g", "w_out": f"{p}.mix.o",
              "q_norm": f"{p}.mix.q.norm", "k_norm": f"{p}.mix.k.norm"})

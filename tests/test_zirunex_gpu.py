@@ -221,6 +221,7 @@ ATTENTION_SHAPES = [
     (2, 1, 128, 128, 130, 3, 16),
     (6, 2, 32, 32, 20, 2, 8),      # three query heads a kv head: decoded rows go through the prefill kernel
     (5, 5, 48, 48, 33, 1, 16),
+    (6, 2, 64, 64, 50, 3, 16),     # the same on the tcgen05 kernel
 ]
 
 
@@ -292,6 +293,21 @@ def test_head_size_64_on_both_prefill_kernels(page):
         name = "attention_prefill_tc" if tc else "attention_prefill"
         assert after.get(name, 0) - before.get(name, 0) == 9, (tc, before, after)
     assert ops.device_errors(DEV) == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dim", [32, 64])
+def test_a_far_key_among_hundreds(dtype, dim):
+    """With a window that holds the whole sequence, one key hundreds of positions back (on another page, in
+    another key tile, in another slice of a decoded row's keys) decides the output; at every page's border."""
+    page = 16
+    for distance in (200, 208, 209, 223, 224, 500):
+        for lengths, new_rows, row in (((531, 40), (1, 1), 0), ((531, 40), (300, 2), 299)):
+            out, want = _attention_case(dtype, 2, 1, dim, dim, 4000, 0, page, lengths, new_rows, seed=23, plant=(0, row, distance))
+            a, b = out[0][row], want[0][row]
+            tol = 1e-4 if dtype == torch.float32 else 2e-2
+            assert float((a - b).abs().max()) <= tol * max(1.0, float(b.abs().max())), (distance, new_rows)
+            assert float(b[:dim].abs().max()) > 5.0 and float(a[:dim].abs().max()) > 5.0, (distance, new_rows)
 
 
 def test_the_fast_kernels_are_the_ones_that_run():
