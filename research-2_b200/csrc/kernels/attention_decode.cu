@@ -600,7 +600,11 @@ extern "C" int r2_attention_decode(const void* q, int q_row_stride, void* out, i
   switch (n_heads / n_kv_heads) {
     case 1: status = launch<1>(p, n_rows, stream); break;
     case 2: status = launch<2>(p, n_rows, stream); break;
+    case 3: status = launch<3>(p, n_rows, stream); break;
     case 4: status = launch<4>(p, n_rows, stream); break;
+    case 5: status = launch<5>(p, n_rows, stream); break;
+    case 6: status = launch<6>(p, n_rows, stream); break;
+    case 7: status = launch<7>(p, n_rows, stream); break;
     case 8: status = launch<8>(p, n_rows, stream); break;
     default: return R2_UNSUPPORTED;
   }
@@ -659,7 +663,11 @@ extern "C" int r2_attention_decode_fused(const void* q, int q_row_stride, void* 
   switch (n_heads / n_kv_heads) {
     case 1: return launch_fused<1>(p, n_rows, stream);
     case 2: return launch_fused<2>(p, n_rows, stream);
+    case 3: return launch_fused<3>(p, n_rows, stream);
     case 4: return launch_fused<4>(p, n_rows, stream);
+    case 5: return launch_fused<5>(p, n_rows, stream);
+    case 6: return launch_fused<6>(p, n_rows, stream);
+    case 7: return launch_fused<7>(p, n_rows, stream);
     case 8: return launch_fused<8>(p, n_rows, stream);
     default: return R2_UNSUPPORTED;
   }

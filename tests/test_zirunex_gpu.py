@@ -219,9 +219,9 @@ ATTENTION_SHAPES = [
     (2, 2, 16, 16, 5, 0, 8),
     (3, 1, 24, 40, 9, 12, 4),      # only the general kernel takes it
     (2, 1, 128, 128, 130, 3, 16),
-    (6, 2, 32, 32, 20, 2, 8),      # three query heads a kv head: decoded rows go through the prefill kernel
+    (6, 2, 32, 32, 20, 2, 8),      # three query heads a kv head
     (5, 5, 48, 48, 33, 1, 16),
-    (6, 2, 64, 64, 50, 3, 16),     # the same on the tcgen05 kernel
+    (6, 2, 64, 64, 50, 3, 16),     # the same at the tcgen05 kernel's head size
 ]
 
 
