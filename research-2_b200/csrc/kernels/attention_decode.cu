@@ -96,7 +96,9 @@ bool g_decode_mma = true;              // r2_attention_decode_set_mma (tests com
 // A tile then costs a warp 32 mma and 16 ldmatrix instead of some 500 scalar instructions, which
 // is what bounds this kernel at large batches (at batch 64 it read the cache at 0.57 of the copy
 // bandwidth with the scalar form).
-template <int G, bool MMA>
+// X: the form with kept first keys, a sink, a gate and two-term weights; without it those parameters are not
+// read and the plain form compiles to what it was.
+template <int G, bool MMA, bool X>
 __global__ void __launch_bounds__(WARPS * 32, (MMA && HD <= 64) ? 5 : 1)  // five CTAs to an SM is what the tiles' shared memory allows
 decode_kernel(const DecodeParams p) {
   pdl_launch_dependents();  // the next kernel may begin its prologue
@@ -120,10 +122,10 @@ decode_kernel(const DecodeParams p) {
   const int first = p.window > 0 ? (pos - p.window + 1 > 0 ? pos - p.window + 1 : 0) : 0;
   // The keys that the row sees are walked by a running index v: first the kept first keys (those below
   // the window's start), then the window's. Key v of the walk lies at position v, or first + (v - kept).
-  const int kept = p.window > 0 ? min(p.keep_first, first) : 0;
+  const int kept = (X && p.window > 0) ? min(p.keep_first, first) : 0;
   const int n_keys = kept + last - first + 1;
   const int v_of_pos = kept + pos - first;   // where the newest key stands in the walk
-  auto key_at = [&](int v) { return v < kept ? v : first + (v - kept); };
+  auto key_at = [&](int v) { return (X && v < kept) ? v : first + (v - kept); };
   // this slice's keys: equal runs of whole 32-key tiles
   const int tiles = (n_keys + 31) / 32;
   const int tiles_per = (tiles + p.n_slices - 1) / p.n_slices;
@@ -323,7 +325,7 @@ decode_kernel(const DecodeParams p) {
         const uint32_t a2 = pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]), a3 = pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
         // what the rounding to bfloat16 left of each weight, as a second bfloat16 operand
         uint32_t r0 = 0, r1 = 0, r2 = 0, r3 = 0;
-        if (p.split_p) {
+        if (X && p.split_p) {
           r0 = pack_rest(sc[2 * kk][0], sc[2 * kk][1], a0); r1 = pack_rest(sc[2 * kk][2], sc[2 * kk][3], a1);
           r2 = pack_rest(sc[2 * kk + 1][0], sc[2 * kk + 1][1], a2); r3 = pack_rest(sc[2 * kk + 1][2], sc[2 * kk + 1][3], a3);
         }
@@ -334,7 +336,7 @@ decode_kernel(const DecodeParams p) {
           ldmatrix_x4_trans(vt + uint32_t(key * ROW_BYTES + (dp * 2 + (lane >> 4)) * 16), b0, b1, b2, b3);
           mma_bf16(o[2 * dp], a0, a1, a2, a3, b0, b1);
           mma_bf16(o[2 * dp + 1], a0, a1, a2, a3, b2, b3);
-          if (p.split_p) {
+          if (X && p.split_p) {
             mma_bf16(o[2 * dp], r0, r1, r2, r3, b0, b1);
             mma_bf16(o[2 * dp + 1], r0, r1, r2, r3, b2, b3);
           }
@@ -462,8 +464,8 @@ decode_kernel(const DecodeParams p) {
       }
     }
     if (p.n_slices == 1) {
-      const bf16* gate = p.gate != nullptr ? p.gate + size_t(t) * p.gate_row_stride + size_t(h0 + g) * HD + d : nullptr;
-      p.out[size_t(t) * p.out_row_stride + size_t(h0 + g) * HD + d] = __float2bfloat16_rn(finish(o, lsum, mx, p.sink, gate));
+      const bf16* gate = (X && p.gate != nullptr) ? p.gate + size_t(t) * p.gate_row_stride + size_t(h0 + g) * HD + d : nullptr;
+      p.out[size_t(t) * p.out_row_stride + size_t(h0 + g) * HD + d] = __float2bfloat16_rn(finish(o, lsum, mx, X ? p.sink : 0, gate));
     } else {
       size_t at = (size_t(t) * p.n_heads + h0 + g) * p.n_slices + slice;
       p.part_o[at * HD + d] = o;
@@ -499,8 +501,8 @@ decode_kernel(const DecodeParams p) {
             lsum += c * __ldcg(&p.part_ml[(base + s) * 2 + 1]);
           }
         }
-        const bf16* gate = p.gate != nullptr ? p.gate + size_t(t) * p.gate_row_stride + size_t(h0 + g) * HD + d : nullptr;
-        p.out[size_t(t) * p.out_row_stride + size_t(h0 + g) * HD + d] = __float2bfloat16_rn(finish(o, lsum, mx, p.sink, gate));
+        const bf16* gate = (X && p.gate != nullptr) ? p.gate + size_t(t) * p.gate_row_stride + size_t(h0 + g) * HD + d : nullptr;
+        p.out[size_t(t) * p.out_row_stride + size_t(h0 + g) * HD + d] = __float2bfloat16_rn(finish(o, lsum, mx, X ? p.sink : 0, gate));
       }
     }
   }
@@ -530,7 +532,7 @@ __global__ void merge_kernel(const float* __restrict__ part_o, const float* __re
   }
 }
 
-template <int G, bool MMA>
+template <int G, bool MMA, bool X>
 bool configure_smem() {
   // once per kernel instance and device (function attributes belong to a device's context): room for
   // the tiles beyond the default 48 KB
@@ -539,28 +541,28 @@ bool configure_smem() {
   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return false;
   bool& done = done_on[device];
   if (!done) {
-    if (cudaFuncSetAttribute(decode_kernel<G, MMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, TILE_SMEM) != cudaSuccess) return false;
+    if (cudaFuncSetAttribute(decode_kernel<G, MMA, X>, cudaFuncAttributeMaxDynamicSharedMemorySize, TILE_SMEM) != cudaSuccess) return false;
     // the CTAs hide each other's waits: ask for the shared memory that lets as many as fit be resident
-    if (cudaFuncSetAttribute(decode_kernel<G, MMA>, cudaFuncAttributePreferredSharedMemoryCarveout, 100) != cudaSuccess) return false;
+    if (cudaFuncSetAttribute(decode_kernel<G, MMA, X>, cudaFuncAttributePreferredSharedMemoryCarveout, 100) != cudaSuccess) return false;
     done = true;
   }
   return true;
 }
 
-template <int G, bool MMA>
+template <int G, bool MMA, bool X>
 int launch_form(const DecodeParams& p, int n_rows, cudaStream_t stream) {
   dim3 grid(p.n_slices, p.n_kv_heads, n_rows);
-  if (!configure_smem<G, MMA>()) return R2_UNSUPPORTED;
-  r2_launch(decode_kernel<G, MMA>, dim3(grid), dim3(WARPS * 32), size_t(TILE_SMEM), stream, p);
+  if (!configure_smem<G, MMA, X>()) return R2_UNSUPPORTED;
+  r2_launch(decode_kernel<G, MMA, X>, dim3(grid), dim3(WARPS * 32), size_t(TILE_SMEM), stream, p);
   return launch_status();
 }
 
-template <int G>
+template <int G, bool X = false>
 int launch(const DecodeParams& p, int n_rows, cudaStream_t stream) {
   if constexpr (MMA_FITS) {
-    if (g_decode_mma) return launch_form<G, true>(p, n_rows, stream);
+    if (g_decode_mma) return launch_form<G, true, X>(p, n_rows, stream);
   }
-  return launch_form<G, false>(p, n_rows, stream);
+  return launch_form<G, false, X>(p, n_rows, stream);
 }
 
 }  // namespace
@@ -600,11 +602,7 @@ extern "C" int r2_attention_decode(const void* q, int q_row_stride, void* out, i
   switch (n_heads / n_kv_heads) {
     case 1: status = launch<1>(p, n_rows, stream); break;
     case 2: status = launch<2>(p, n_rows, stream); break;
-    case 3: status = launch<3>(p, n_rows, stream); break;
     case 4: status = launch<4>(p, n_rows, stream); break;
-    case 5: status = launch<5>(p, n_rows, stream); break;
-    case 6: status = launch<6>(p, n_rows, stream); break;
-    case 7: status = launch<7>(p, n_rows, stream); break;
     case 8: status = launch<8>(p, n_rows, stream); break;
     default: return R2_UNSUPPORTED;
   }
@@ -616,8 +614,15 @@ extern "C" int r2_attention_decode(const void* q, int q_row_stride, void* out, i
 
 namespace {
 
+// The plain form for groups of 1, 2, 4 and 8 query heads; the form with extras for every group up to 8.
 template <int G>
-int launch_fused(const DecodeParams& p, int n_rows, cudaStream_t stream) { return launch<G>(p, n_rows, stream); }
+int launch_fused(const DecodeParams& p, int n_rows, cudaStream_t stream) {
+  const bool extras = p.keep_first > 0 || p.sink != 0 || p.gate != nullptr || p.split_p != 0;
+  if constexpr (G == 1 || G == 2 || G == 4 || G == 8) {
+    if (!extras) return launch<G, false>(p, n_rows, stream);
+  }
+  return launch<G, true>(p, n_rows, stream);
+}
 
 }  // namespace
 

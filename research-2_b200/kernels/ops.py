@@ -693,7 +693,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     # first keys, a sink and an output gate are taken by both prefill kernels and the fused decode kernel
     fits = v_head_dim == head_dim and head_dim % 16 == 0
     plain = fits and keep_first == 0 and not sink and gate is None
-    if plain and q.dtype == torch.bfloat16 and decode_only and _fast_attention and 1 <= group <= 8:
+    if plain and q.dtype == torch.bfloat16 and decode_only and _fast_attention and group in (1, 2, 4, 8):
         lib = _lib_for_head_dim("attention_decode", head_dim)
         n_slices = decode_slices(n, n_kv_heads, max_context, q.device)
         ws = _workspace(q.device)
