@@ -214,7 +214,7 @@ def _attention_case(dtype, n_heads, n_kv, dim, vdim, window, keep, page, lengths
 
 ATTENTION_SHAPES = [
     # heads, kv heads, dim, vdim, window, kept, page
-    (4, 2, 32, 32, 40, 6, 16),
+    (4, 2, 32, 32, 44, 7, 16),
     (8, 1, 64, 64, 70, 70, 32),
     (2, 2, 16, 16, 5, 0, 8),
     (3, 1, 24, 40, 9, 12, 4),      # only the general kernel takes it
@@ -246,7 +246,7 @@ def test_one_key_that_stands_out_at_every_edge(dtype, decode, dim):
     the row's first head returns (nearly) that value, one place further out it returns an ordinary
     mixture; the same at the last kept first token and the first one that is not kept; for rows in a
     prompt's portion and for decoded rows, with the key far behind a page's border."""
-    heads, kv, window, keep, page = 2, 1, 40, 6, 16   # (head size 64 in bfloat16: the tcgen05 kernel)
+    heads, kv, window, keep, page = 2, 1, 36, 5, 16   # (head size 64 in bfloat16: the tcgen05 kernel)
     n = 230
     for row_pos, distance, seen in (
         (n - 1, window - 1, True), (n - 1, window, False),              # the window's far edge
@@ -314,8 +314,8 @@ def test_the_fast_kernels_are_the_ones_that_run():
     from research_2_b200.kernels import ops
 
     before = ops.kernel_uses()
-    _attention_case(torch.bfloat16, 4, 2, 32, 32, 40, 6, 16, (150, 37), (150, 2), seed=1)
-    _attention_case(torch.bfloat16, 4, 2, 32, 32, 40, 6, 16, (150, 37), (1, 1), seed=1)
+    _attention_case(torch.bfloat16, 4, 2, 32, 32, 44, 7, 16, (150, 37), (150, 2), seed=1)
+    _attention_case(torch.bfloat16, 4, 2, 32, 32, 44, 7, 16, (150, 37), (1, 1), seed=1)
     _attention_case(torch.bfloat16, 3, 1, 24, 40, 9, 12, 4, (30, 7), (30, 2), seed=1)
     after = ops.kernel_uses()
     grew = {k: after.get(k, 0) - before.get(k, 0) for k in after}
