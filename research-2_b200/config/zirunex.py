@@ -4,9 +4,12 @@ A Zirunex config.json names its model with `"architecture": "Zirunex"` and lists
 by one: every entry of `layers` gives the layer's `type` (which mixer it has), the mixer's sizes
 and constants (`mixer`), its feed-forward (`mlp`, or null for a layer without one), and
 optionally `weights_of: j` for a layer that runs with layer j's tensors and a cache of its own.
-Beside the layers stand `vocab`, `width`, `norm.eps` and `embedding.scale`. No size or constant
-has a default here: a key that is missing is an error that names it. The design has no limit on
-a sequence's length (positions enter nothing but the mask), so the configuration has none.
+Beside the layers stand `vocab`, `width`, `norm.eps` and `embedding.scale`. No size has a default
+here: a size that is missing is an error that names it. A mechanism that a file does not mention
+is not there: no `mlp` is no feed-forward, no `mask` (or no `mask.size`) is no window, no
+`mask.keep_first` is no kept token, no `embedding` is a scale of one; `kv_heads` and `vdim` left out
+equal `heads` and `dim`. The design has no limit on a sequence's length (positions enter nothing but
+the mask), so the configuration has none.
 """
 
 from __future__ import annotations
@@ -17,6 +20,7 @@ from dataclasses import dataclass
 from .registry import ConfigError
 
 NAME = "Zirunex"
+NO_WINDOW = 1 << 30  # a window that no sequence reaches: every earlier position is seen
 MIXER_TYPES = ("attention",)
 MLP_KINDS = ("dense",)
 
@@ -60,14 +64,21 @@ class AttentionMixer:
 
     @staticmethod
     def from_json(data: dict, where: str) -> "AttentionMixer":
-        mask = _get(data, "mask", where)
-        heads, kv_heads = _int(data, "heads", where), _int(data, "kv_heads", where)
+        mask = data.get("mask") if isinstance(data, dict) else None
+        if mask is None:
+            mask = {}
+        if not isinstance(mask, dict):
+            raise ConfigError(f"config.json: {where}'mask' must be an object, got {mask!r}")
+        heads = _int(data, "heads", where)
+        kv_heads = _int(data, "kv_heads", where) if "kv_heads" in data else heads
         if heads % kv_heads != 0:
             raise ConfigError(f"config.json: {where}'heads' ({heads}) is not a multiple of 'kv_heads' ({kv_heads})")
         return AttentionMixer(
-            heads=heads, kv_heads=kv_heads, dim=_int(data, "dim", where), vdim=_int(data, "vdim", where),
-            scale=_number(data, "scale", where), window=_int(mask, "size", where + "mask."),
-            keep_first=_int(mask, "keep_first", where + "mask.", minimum=0))
+            heads=heads, kv_heads=kv_heads, dim=_int(data, "dim", where),
+            vdim=_int(data, "vdim", where) if "vdim" in data else _int(data, "dim", where),
+            scale=_number(data, "scale", where),
+            window=min(_int(mask, "size", where + "mask."), NO_WINDOW) if mask.get("size") is not None else NO_WINDOW,
+            keep_first=min(_int(mask, "keep_first", where + "mask.", minimum=0), NO_WINDOW) if mask.get("keep_first") is not None else 0)
 
     def to_json(self) -> dict:
         return {"dim": self.dim, "heads": self.heads, "kv_heads": self.kv_heads,
@@ -125,7 +136,7 @@ class ZirunexConfig:
             if kind not in MIXER_TYPES:
                 raise ConfigError(f"config.json: {where}'type' {kind!r} is not supported (supported: {', '.join(MIXER_TYPES)})")
             mixer = AttentionMixer.from_json(_get(entry, "mixer", where), where + "mixer.")
-            mlp_json = _get(entry, "mlp", where)
+            mlp_json = entry.get("mlp")
             mlp = None if mlp_json is None else DenseMlp.from_json(mlp_json, where + "mlp.")
             owner = entry.get("weights_of")
             if owner is not None:
@@ -148,7 +159,7 @@ class ZirunexConfig:
         return ZirunexConfig(
             vocab_size=_int(data, "vocab", ""), width=_int(data, "width", ""),
             norm_eps=_number(_get(data, "norm", ""), "eps", "norm."),
-            embedding_scale=_number(_get(data, "embedding", ""), "scale", "embedding.", positive=False),
+            embedding_scale=_number(data["embedding"], "scale", "embedding.", positive=False) if data.get("embedding") is not None else 1.0,
             layers=tuple(layers))
 
     def to_json(self) -> dict:

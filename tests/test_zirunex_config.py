@@ -36,13 +36,13 @@ def test_config_is_read_key_by_key():
 @pytest.mark.parametrize("path, value, message", [
     (("vocab",), None, "'vocab' is missing"),
     (("norm", "eps"), -1.0, "must be positive"),
-    (("layers", 0, "mixer", "mask", "size"), None, "mask.'size' is missing"),
+    (("layers", 0, "mixer", "dim"), None, "mixer.'dim' is missing"),
+    (("layers", 0, "mixer", "scale"), None, "mixer.'scale' is missing"),
     (("layers", 0, "mixer", "kv_heads"), 3, "not a multiple"),
     (("layers", 0, "type"), "recurrent", "not supported"),
     (("layers", 0, "mlp", "kind"), "routed", "not supported"),
     (("layers", 2, "weights_of"), 2, "must name another layer"),
     (("layers", 2, "mlp", "ff"), 80, "describes another layer"),
-    (("layers", 1, "mlp"), "absent", "'mlp' is missing"),
 ])
 def test_config_errors_name_the_key(path, value, message):
     data = copy.deepcopy(CASES["a"]["config"])
@@ -55,6 +55,21 @@ def test_config_errors_name_the_key(path, value, message):
         at[path[-1]] = value
     with pytest.raises(ConfigError, match=message):
         ZirunexConfig.from_json(data)
+
+
+def test_what_a_file_does_not_mention_is_not_there():
+    data = copy.deepcopy(CASES["d"]["config"])
+    layer = data["layers"][1]
+    layer["mixer"] = copy.deepcopy(layer["mixer"])   # (the cases' layers share their mixer entries)
+    del layer["mlp"], layer["mixer"]["mask"], layer["mixer"]["kv_heads"], layer["mixer"]["vdim"]
+    del data["embedding"]
+    del data["layers"][0]["mixer"]["mask"]["keep_first"]
+    cfg = ZirunexConfig.from_json(data)
+    bare = cfg.layers[1]
+    assert bare.mlp is None and bare.mixer.kv_heads == bare.mixer.heads == 4 and bare.mixer.vdim == bare.mixer.dim == 32
+    assert bare.mixer.window >= 1 << 30 and bare.mixer.keep_first == 0 and cfg.embedding_scale == 1.0
+    assert cfg.layers[0].mixer.window == 33 and cfg.layers[0].mixer.keep_first == 0
+    assert ZirunexConfig.from_json(cfg.to_json()) == cfg
 
 
 def test_weight_spec_and_model_folder(tmp_path):
