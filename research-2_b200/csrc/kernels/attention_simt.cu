@@ -28,7 +28,8 @@ attention_simt_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict__
                       const int32_t* __restrict__ row_entry, const int32_t* __restrict__ positions,
                       const int32_t* __restrict__ seq_lens, int n_heads, int n_kv_heads, int head_dim, int v_head_dim,
                       float scale, int window, int keep_first, int sink, const T* __restrict__ gate, int gate_row_stride,
-                      int n_pages) {
+                      int n_pages, float softcap, const float* __restrict__ sinks, const float* __restrict__ head_gate,
+                      int head_gate_stride) {
   pdl_launch_dependents();  // the next kernel may begin its prologue
   pdl_wait();               // the previous kernel's writes are visible from here on
   __shared__ float q_s[WARPS][MAX_HEAD_DIM];
@@ -55,7 +56,8 @@ attention_simt_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict__
   // With a window, the sequence's first `keep_first` keys stay visible: they are walked first, as a
   // range of their own, so that the walk depends on the row's position alone.
   const int kept = window > 0 ? (keep_first < first ? keep_first : first) : 0;
-  float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;   // a sink: an extra exp(0) term in the sum, nothing in the output
+  // a sink: an extra term in the sum and nothing in the output; exp(0), or exp(sinks[h]) where heads have learned ones
+  float m = sinks != nullptr ? sinks[h] : (sink ? 0.f : -INFINITY), l = (sink || sinks != nullptr) ? 1.f : 0.f;
   float acc[MAX_HEAD_DIM / 32];
 #pragma unroll
   for (int i = 0; i < MAX_HEAD_DIM / 32; ++i) acc[i] = 0.f;
@@ -75,6 +77,7 @@ attention_simt_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict__
         float dot = 0.f;
         for (int d = 0; d < head_dim; ++d) dot = fmaf(q_s[warp][d], to_float(kr[d]), dot);
         s = dot * scale;
+        if (softcap > 0.f) s = softcap * tanhf(s / softcap);   // scores are capped before the softmax
       }
       float m_new = fmaxf(m, warp_max(s));
       float corr = expf(m - m_new);  // exp(-inf) = 0 on the first tile
@@ -100,6 +103,8 @@ attention_simt_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict__
   }
   float inv = l > 0.f ? 1.f / l : 0.f;
   const T* gr = gate != nullptr ? gate + size_t(t) * gate_row_stride + size_t(h) * v_head_dim : nullptr;
+  // one gate per head: sigmoid of a float logit
+  if (head_gate != nullptr) inv *= 1.f / (1.f + expf(-head_gate[size_t(t) * head_gate_stride + h]));
 #pragma unroll
   for (int i = 0; i < MAX_HEAD_DIM / 32; ++i) {
     int d = lane + 32 * i;
@@ -117,13 +122,16 @@ attention_simt_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict__
 // out [T, n_heads * v_head_dim]; the cache of this layer as in r2_kv_write. `window` > 0 limits a row
 // at position p to the keys (p - window, p] and, with `keep_first`, the sequence's first keep_first keys;
 // `sink` adds one to the softmax's denominator; `gate` (may be null; [T, n_heads * v_head_dim] with its
-// own row stride) multiplies the output by its sigmoid.
+// own row stride) multiplies the output by its sigmoid. `softcap` > 0 caps the scaled scores (cap * tanh(s / cap));
+// `sinks` (may be null; float [n_heads]) puts exp(sinks[h]) into head h's denominator; `head_gate` (may be null; float
+// [T, n_heads] with its own row stride) multiplies head h's output by the sigmoid of its entry.
 extern "C" int r2_attention_simt(const void* q, int q_row_stride, void* out, int out_row_stride, const void* k_cache,
                                  const void* v_cache, long long page_stride, int page_size,
                                  const int32_t* block_tables, int table_width, const int32_t* row_entry,
                                  const int32_t* positions, const int32_t* seq_lens, int n_rows, int n_heads,
                                  int n_kv_heads, int head_dim, int v_head_dim, float scale, int window, int keep_first,
                                  int sink, const void* gate, int gate_row_stride, int n_pages, int dtype,
+                                 float softcap, const float* sinks, const float* head_gate, int head_gate_stride,
                                  cudaStream_t stream) {
   if (n_rows <= 0) return R2_OK;
   if (head_dim < 1 || head_dim > MAX_HEAD_DIM || v_head_dim < 1 || v_head_dim > MAX_HEAD_DIM) return R2_UNSUPPORTED;
@@ -133,12 +141,12 @@ extern "C" int r2_attention_simt(const void* q, int q_row_stride, void* out, int
     r2_launch(attention_simt_kernel<float>, dim3(grid), dim3(WARPS * 32), size_t(0), stream,
         (const float*)q, q_row_stride, (float*)out, out_row_stride, (const float*)k_cache, (const float*)v_cache,
         page_stride, page_size, block_tables, table_width, row_entry, positions, seq_lens, n_heads, n_kv_heads,
-        head_dim, v_head_dim, scale, window, keep_first, sink, (const float*)gate, gate_row_stride, n_pages);
+        head_dim, v_head_dim, scale, window, keep_first, sink, (const float*)gate, gate_row_stride, n_pages, softcap, sinks, head_gate, head_gate_stride);
   } else if (dtype == R2_BF16) {
     r2_launch(attention_simt_kernel<bf16>, dim3(grid), dim3(WARPS * 32), size_t(0), stream,
         (const bf16*)q, q_row_stride, (bf16*)out, out_row_stride, (const bf16*)k_cache, (const bf16*)v_cache,
         page_stride, page_size, block_tables, table_width, row_entry, positions, seq_lens, n_heads, n_kv_heads,
-        head_dim, v_head_dim, scale, window, keep_first, sink, (const bf16*)gate, gate_row_stride, n_pages);
+        head_dim, v_head_dim, scale, window, keep_first, sink, (const bf16*)gate, gate_row_stride, n_pages, softcap, sinks, head_gate, head_gate_stride);
   } else {
     return R2_BAD_DTYPE;
   }

@@ -640,3 +640,74 @@ extern "C" int r2_gated_act(const void* gate_up, int in_stride, void* out, int o
   }
   return launch_status();
 }
+
+// ---- rotation of query and key heads by position -------------------------------------------------
+// In place on the first n_heads heads of every row of `buf` (a stacked projection: query heads, then key heads).
+// Of each head the first rot_dims dimensions are rotated, dimension i with dimension i + rot_dims / 2: the pair (u, v)
+// at position p becomes (u cos a - v sin a, v cos a + u sin a), a = p * inv_freq[i]. Positions and angles are float.
+namespace {
+template <typename T>
+__global__ void __launch_bounds__(256)
+rotate_half_kernel(T* __restrict__ buf, int row_stride, int n_heads, int head_dim, int half, const float* __restrict__ inv_freq,
+                   const int32_t* __restrict__ positions) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const float p = float(positions[t]);
+  T* row = buf + size_t(t) * row_stride;
+  for (int idx = blockIdx.y * blockDim.x + threadIdx.x; idx < n_heads * half; idx += gridDim.y * blockDim.x) {
+    const int head = idx / half, i = idx - head * half;
+    float s, c;
+    sincosf(p * inv_freq[i], &s, &c);
+    T* x = row + size_t(head) * head_dim;
+    const float u = to_float(x[i]), v = to_float(x[i + half]);
+    x[i] = from_float<T>(u * c - v * s);
+    x[i + half] = from_float<T>(v * c + u * s);
+  }
+}
+
+// out = x + weight_sum * (a / rms(a) * wa + b / rms(b) * wb): two branches' outputs, each normalised over the row with a
+// gain of its own, join the residual stream. All float.
+__global__ void __launch_bounds__(256)
+pair_norm_add_kernel(const float* __restrict__ x, const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ wa,
+                     const float* __restrict__ wb, float* __restrict__ out, int width, float eps, float share) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[33];
+  const size_t at = size_t(blockIdx.x) * width;
+  float sa = 0.f, sb = 0.f;
+  for (int d = threadIdx.x; d < width; d += blockDim.x) {
+    const float va = a[at + d], vb = b[at + d];
+    sa = fmaf(va, va, sa);
+    sb = fmaf(vb, vb, sb);
+  }
+  const float inv_a = 1.f / sqrtf(block_sum(sa, scratch) / float(width) + eps);
+  const float inv_b = 1.f / sqrtf(block_sum(sb, scratch) / float(width) + eps);
+  for (int d = threadIdx.x; d < width; d += blockDim.x)
+    out[at + d] = x[at + d] + share * (a[at + d] * inv_a * wa[d] + b[at + d] * inv_b * wb[d]);
+}
+}  // namespace
+
+extern "C" int r2_rotate_half(void* buf, int row_stride, int n_rows, int n_heads, int head_dim, int rot_dims, const float* inv_freq,
+                              const int32_t* positions, int dtype, cudaStream_t stream) {
+  if (n_rows <= 0 || rot_dims == 0) return R2_OK;
+  if (n_heads < 1 || rot_dims < 0 || rot_dims % 2 != 0 || rot_dims > head_dim) return R2_BAD_SHAPE;
+  const int half = rot_dims / 2;
+  dim3 grid(n_rows, (n_heads * half + 1023) / 1024);
+  if (dtype == R2_F32) {
+    r2_launch(rotate_half_kernel<float>, grid, dim3(256), size_t(0), stream, (float*)buf, row_stride, n_heads, head_dim, half, inv_freq, positions);
+  } else if (dtype == R2_BF16) {
+    r2_launch(rotate_half_kernel<bf16>, grid, dim3(256), size_t(0), stream, (bf16*)buf, row_stride, n_heads, head_dim, half, inv_freq, positions);
+  } else {
+    return R2_BAD_DTYPE;
+  }
+  return launch_status();
+}
+
+extern "C" int r2_pair_norm_add(const float* x, const float* a, const float* b, const float* wa, const float* wb, float* out,
+                                int n_rows, int width, float eps, float share, cudaStream_t stream) {
+  if (n_rows <= 0) return R2_OK;
+  if (width < 1) return R2_BAD_SHAPE;
+  r2_launch(pair_norm_add_kernel, dim3(n_rows), dim3(256), size_t(0), stream, x, a, b, wa, wb, out, width, eps, share);
+  return launch_status();
+}

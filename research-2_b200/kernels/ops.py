@@ -474,6 +474,231 @@ def gated_act(gate_up: torch.Tensor, limit: float, alpha: float, up_offset: floa
     return out
 
 
+def expert_act(gate_up: torch.Tensor, kind: str, limit: float = 0.0, alpha: float = 1.0, up_offset: float = 0.0,
+               route: torch.Tensor | None = None, n_experts: int = 0, expert_width: int = 0, tail_limit: float | None = None,
+               out: torch.Tensor | None = None) -> torch.Tensor:
+    """The inner activation of gated feed-forwards whose projections lie side by side: a row of `gate_up` [T, 2 F] holds
+    the gates of all F columns and then their ups. kind "relu": relu(g) * u. kind "clamped_swish": g' sigmoid(alpha g')
+    (u' + up_offset) with g' = min(g, limit), u' = clamp(u, -limit, limit). With `route` (float32 [T, n_experts], zero
+    for experts that a row does not use) the first n_experts * expert_width columns are the routed experts', each
+    multiplied by the row's weight for its expert; the columns after them belong to an expert that every row uses
+    (limit `tail_limit`). -> [T, F] in the same dtype."""
+    _need(gate_up, "gate_up", dim=2)
+    if gate_up.shape[1] % 2:
+        raise KernelError(f"expert_act: {tuple(gate_up.shape)} does not hold a gate and an up half")
+    kinds = {"clamped_swish": 0, "relu": 1}
+    if kind not in kinds:
+        raise KernelError(f"expert_act: unknown kind {kind!r}; known: {sorted(kinds)}")
+    inner = gate_up.shape[1] // 2
+    if route is not None:
+        _need(route, "route", torch.float32, 2)
+        if route.shape != (gate_up.shape[0], n_experts) or not route.is_contiguous() or n_experts * expert_width > inner:
+            raise KernelError(f"expert_act: route {tuple(route.shape)} does not fit {n_experts} experts of {expert_width} in {inner} columns")
+    else:
+        n_experts = 0
+    if out is None:
+        out = torch.empty(gate_up.shape[0], inner, dtype=gate_up.dtype, device=gate_up.device)
+    status = _lib("routing").r2_expert_act(
+        _p(gate_up), _rows(gate_up, "gate_up"), _p(out), _rows(out, "out"), gate_up.shape[0], inner, kinds[kind],
+        C.c_float(limit), C.c_float(alpha), C.c_float(up_offset), _p(route), n_experts, expert_width,
+        C.c_float(limit if tail_limit is None else tail_limit), dtype_code(gate_up.dtype), _stream())
+    _check(status, "expert_act")
+    return out
+
+
+def small_linear(h: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """h [T, K] (any compute dtype) times w [N, K] float32 (+ bias float32) -> float32 [T, N]: the few outputs per row
+    that must stay in 32-bit (gates of a recurrence, one gate per head, step sizes), each one warp's sum."""
+    _need(h, "h", dim=2)
+    _need(w, "w", torch.float32, 2)
+    if w.shape[1] != h.shape[1] or not w.is_contiguous():
+        raise KernelError(f"small_linear: h {tuple(h.shape)} does not fit w {tuple(w.shape)}")
+    if bias is not None:
+        _need(bias, "bias", torch.float32, 1)
+        if bias.shape[0] != w.shape[0]:
+            raise KernelError(f"small_linear: bias {tuple(bias.shape)} does not fit {w.shape[0]} outputs")
+    if out is None:
+        out = torch.empty(h.shape[0], w.shape[0], dtype=torch.float32, device=h.device)
+    status = _lib("routing").r2_small_linear(_p(h), _rows(h, "h"), _p(w), _p(bias), _p(out), _rows(out, "out"), h.shape[0],
+                                            w.shape[0], h.shape[1], dtype_code(h.dtype), _stream())
+    _check(status, "small_linear")
+    return out
+
+
+def route_top_k(h: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, top: int):
+    """Router: logits h @ w^T + bias in float32, the `top` largest per row (the lower index wins a tie), softmax over
+    the chosen logits only. -> (dense float32 [T, experts]: a row's weights, zero for experts not chosen;
+    chosen int32 [T, top]; their weights float32 [T, top])."""
+    _need(h, "h", dim=2)
+    _need(w, "w", torch.float32, 2)
+    if w.shape[1] != h.shape[1] or not w.is_contiguous() or not 1 <= top <= w.shape[0]:
+        raise KernelError(f"route_top_k: h {tuple(h.shape)}, w {tuple(w.shape)}, top {top} do not fit")
+    if bias is not None:
+        _need(bias, "bias", torch.float32, 1)
+    n, e = h.shape[0], w.shape[0]
+    dense = torch.empty(n, e, dtype=torch.float32, device=h.device)
+    chosen = torch.empty(n, top, dtype=torch.int32, device=h.device)
+    weight = torch.empty(n, top, dtype=torch.float32, device=h.device)
+    status = _lib("routing").r2_route_top_k(_p(h), _rows(h, "h"), _p(w), _p(bias), _p(dense), _p(chosen), _p(weight), n, e, top,
+                                           h.shape[1], dtype_code(h.dtype), _stream())
+    _check(status, "route_top_k")
+    return dense, chosen, weight
+
+
+def rotate_half(buf: torch.Tensor, n_heads: int, head_dim: int, rot_dims: int, inv_freq: torch.Tensor, positions: torch.Tensor) -> None:
+    """Rotation by position, in place, of the first `n_heads` heads of every row of `buf` (a stacked projection whose
+    first columns are the query heads and then the key heads): of each head the first rot_dims dimensions, dimension i
+    paired with i + rot_dims / 2, by the angle position * inv_freq[i] (float32 [rot_dims / 2])."""
+    _need(buf, "buf", dim=2)
+    _need(inv_freq, "inv_freq", torch.float32, 1)
+    _need(positions, "positions", torch.int32, 1)
+    if rot_dims % 2 or not 0 <= rot_dims <= head_dim or inv_freq.shape[0] != rot_dims // 2 or buf.shape[1] < n_heads * head_dim:
+        raise KernelError(f"rotate_half: {rot_dims} of {head_dim} dimensions, {n_heads} heads in rows of {buf.shape[1]}")
+    status = _lib("rowwise").r2_rotate_half(_p(buf), _rows(buf, "buf"), buf.shape[0], n_heads, head_dim, rot_dims, _p(inv_freq),
+                                           _p(positions), dtype_code(buf.dtype), _stream())
+    _check(status, "rotate_half")
+
+
+def pair_norm_add(x: torch.Tensor, a: torch.Tensor, b: torch.Tensor, w_a: torch.Tensor, w_b: torch.Tensor, eps: float,
+                  share: float = 0.5) -> torch.Tensor:
+    """x + share * (rms_norm(a) * w_a + rms_norm(b) * w_b), all float32 [T, D]: two branches join the stream."""
+    for name, t in (("x", x), ("a", a), ("b", b)):
+        _need(t, name, torch.float32, 2)
+        if t.shape != x.shape or not t.is_contiguous():
+            raise KernelError(f"pair_norm_add: {name} {tuple(t.shape)} must be contiguous and shaped like x {tuple(x.shape)}")
+    for name, t in (("w_a", w_a), ("w_b", w_b)):
+        _need(t, name, torch.float32, 1)
+        if t.shape[0] != x.shape[1]:
+            raise KernelError(f"pair_norm_add: {name} {tuple(t.shape)} does not fit the width {x.shape[1]}")
+    out = torch.empty_like(x)
+    status = _lib("rowwise").r2_pair_norm_add(_p(x), _p(a), _p(b), _p(w_a), _p(w_b), _p(out), x.shape[0], x.shape[1],
+                                             C.c_float(eps), C.c_float(share), _stream())
+    _check(status, "pair_norm_add")
+    return out
+
+
+def mlstm_state_floats(dim: int, vdim: int) -> int:
+    """Floats of one head's matrix-memory state in a request slot (matrix, normaliser, running maximum)."""
+    fn = _lib("recurrent").r2_mlstm_state_floats
+    fn.restype = C.c_longlong
+    return int(fn(dim, vdim))
+
+
+def _entries(q_start, state_slot, fresh) -> int:
+    for name, t in (("q_start", q_start), ("state_slot", state_slot), ("fresh", fresh)):
+        _need(t, name, torch.int32, 1)
+    n = q_start.shape[0] - 1
+    if state_slot.shape[0] < n or fresh.shape[0] < n:
+        raise KernelError("entries: state_slot / fresh are shorter than q_start says")
+    return n
+
+
+def mlstm_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gates: torch.Tensor, cap: float, q_scale: float,
+               state: torch.Tensor, q_start: torch.Tensor, state_slot: torch.Tensor, fresh: torch.Tensor, n_heads: int,
+               dim: int, vdim: int) -> torch.Tensor:
+    """The matrix memory's recurrence for every entry of a batch, from and to the entries' state slots.
+    q, k [T, heads * dim], v [T, heads * vdim] (slices of a projection); gates float32 [T, 2 heads]: input gates then
+    forget gates before the cap; state float32 [slots, heads * mlstm_state_floats]. -> float32 [T, heads * vdim], the
+    heads' outputs before their norm."""
+    n = _entries(q_start, state_slot, fresh)
+    for name, t, width in (("q", q, n_heads * dim), ("k", k, n_heads * dim), ("v", v, n_heads * vdim)):
+        _need(t, name, q.dtype, 2)
+        if t.shape[1] != width or t.shape[0] != q.shape[0]:
+            raise KernelError(f"mlstm_scan: {name} {tuple(t.shape)} is not [T, {width}]")
+    _need(gates, "gates", torch.float32, 2)
+    _need(state, "state", torch.float32, 2)
+    per_head = mlstm_state_floats(dim, vdim)
+    if gates.shape != (q.shape[0], 2 * n_heads) or state.shape[1] != n_heads * per_head or not state.is_contiguous():
+        raise KernelError(f"mlstm_scan: gates {tuple(gates.shape)} / state {tuple(state.shape)} do not fit {n_heads} heads of {dim} x {vdim}")
+    out = torch.empty(q.shape[0], n_heads * vdim, dtype=torch.float32, device=q.device)
+    status = _lib("recurrent").r2_mlstm_scan(
+        _p(q), _rows(q, "q"), _p(k), _rows(k, "k"), _p(v), _rows(v, "v"), _p(gates), _rows(gates, "gates"), C.c_float(cap),
+        C.c_float(q_scale), _p(state), C.c_longlong(state.shape[1]), _p(q_start), _p(state_slot), _p(fresh), n, _p(out),
+        _rows(out, "out"), n_heads, dim, vdim, dtype_code(q.dtype), _stream())
+    _check(status, "mlstm_scan")
+    return out
+
+
+def causal_conv(x: torch.Tensor, taps: torch.Tensor, bias: torch.Tensor | None, state: torch.Tensor, conv_state_off: int,
+                row_entry: torch.Tensor, q_start: torch.Tensor, state_slot: torch.Tensor, fresh: torch.Tensor) -> torch.Tensor:
+    """silu of a causal convolution per channel: x [T, C] (a slice of a projection), taps float32 [C, n_taps] whose last
+    column is the current token's. Inputs before an entry's first row come from the request's state slot (float32
+    [slots, floats]; at `conv_state_off` the inputs of the last n_taps - 1 positions, [n_taps - 1, C]), zeros before a
+    sequence's start. The slot is read only: `ssd_scan` renews it. -> [T, C] in x's dtype."""
+    _need(x, "x", dim=2)
+    _need(taps, "taps", torch.float32, 2)
+    _need(state, "state", torch.float32, 2)
+    _entries(q_start, state_slot, fresh)
+    _need(row_entry, "row_entry", torch.int32, 1)
+    channels, n_taps = taps.shape
+    if x.shape[1] != channels or not taps.is_contiguous() or conv_state_off + (n_taps - 1) * channels > state.shape[1]:
+        raise KernelError(f"causal_conv: x {tuple(x.shape)}, taps {tuple(taps.shape)}, state {tuple(state.shape)} do not fit")
+    if bias is not None:
+        _need(bias, "bias", torch.float32, 1)
+    out = torch.empty(x.shape[0], channels, dtype=x.dtype, device=x.device)
+    status = _lib("recurrent").r2_causal_conv(
+        _p(x), _rows(x, "x"), _p(out), _rows(out, "out"), _p(taps), _p(bias), n_taps, channels, _p(state), C.c_longlong(state.shape[1]),
+        C.c_longlong(conv_state_off), _p(row_entry), _p(q_start), _p(state_slot), _p(fresh), x.shape[0], dtype_code(x.dtype), _stream())
+    _check(status, "causal_conv")
+    return out
+
+
+def ssd_scan(x: torch.Tensor, b: torch.Tensor, c: torch.Tensor, steps: torch.Tensor, step_bias: torch.Tensor, log_rate: torch.Tensor,
+             skip: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor, state_slot: torch.Tensor, fresh: torch.Tensor,
+             n_heads: int, n_groups: int, n_state: int, vdim: int, conv_in: torch.Tensor | None = None, conv_taps: int = 1,
+             conv_state_off: int = 0) -> torch.Tensor:
+    """The state-space recurrence S <- exp(-exp(log_rate) dt) S + dt B x^T, y = S^T C + skip x, dt = softplus(steps +
+    step_bias), for every entry of a batch, from and to the entries' state slots. x [T, heads * vdim], b and c
+    [T, groups * n_state]; steps float32 [T, heads]; state float32 [slots, floats]: S [heads, n_state, vdim] first. With
+    `conv_in` (the convolution's input rows of this step, [T, channels]) the convolution's last conv_taps - 1 inputs at
+    `conv_state_off` are renewed too. -> float32 [T, heads * vdim]."""
+    n = _entries(q_start, state_slot, fresh)
+    _need(x, "x", dim=2)
+    _need(b, "b", x.dtype, 2)
+    _need(c, "c", x.dtype, 2)
+    _need(steps, "steps", torch.float32, 2)
+    _need(state, "state", torch.float32, 2)
+    for name, t in (("step_bias", step_bias), ("log_rate", log_rate), ("skip", skip)):
+        _need(t, name, torch.float32, 1)
+        if t.shape[0] != n_heads:
+            raise KernelError(f"ssd_scan: {name} {tuple(t.shape)} is not [{n_heads}]")
+    if (x.shape[1] != n_heads * vdim or b.shape[1] != n_groups * n_state or c.shape[1] != n_groups * n_state
+            or steps.shape != (x.shape[0], n_heads) or n_heads % n_groups or state.shape[1] < n_heads * n_state * vdim):
+        raise KernelError("ssd_scan: shapes do not fit")
+    channels = 0
+    if conv_in is not None:
+        _need(conv_in, "conv_in", x.dtype, 2)
+        channels = conv_in.shape[1]
+        if conv_state_off < n_heads * n_state * vdim or conv_state_off + (conv_taps - 1) * channels > state.shape[1]:
+            raise KernelError("ssd_scan: the convolution's state does not fit the slot")
+    out = torch.empty(x.shape[0], n_heads * vdim, dtype=torch.float32, device=x.device)
+    status = _lib("recurrent").r2_ssd_scan(
+        _p(x), _rows(x, "x"), _p(b), _rows(b, "b"), _p(c), _rows(c, "c"), _p(steps), _rows(steps, "steps"), _p(step_bias),
+        _p(log_rate), _p(skip), _p(state), C.c_longlong(state.shape[1]), _p(q_start), _p(state_slot), _p(fresh), n, _p(out),
+        _rows(out, "out"), n_heads, n_groups, n_state, vdim, _p(conv_in), 0 if conv_in is None else _rows(conv_in, "conv_in"),
+        channels, conv_taps, C.c_longlong(conv_state_off), dtype_code(x.dtype), _stream())
+    _check(status, "ssd_scan")
+    return out
+
+
+def group_norm_gated(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, n_groups: int, eps: float, gate_first: bool,
+                     out_dtype: torch.dtype) -> torch.Tensor:
+    """RMS norm of float32 rows y [T, C] in n_groups equal parts, each by its own root mean square, times weight [C], with
+    a gate [T, C] (a slice of a projection, in out_dtype): `gate_first`: y * silu(gate) is what is normalised; else the
+    normalised, weighted result is multiplied by sigmoid(gate). -> [T, C] in out_dtype."""
+    _need(y, "y", torch.float32, 2)
+    _need(gate, "gate", out_dtype, 2)
+    _need(weight, "weight", torch.float32, 1)
+    if gate.shape != y.shape or weight.shape[0] != y.shape[1] or y.shape[1] % n_groups:
+        raise KernelError(f"group_norm_gated: y {tuple(y.shape)}, gate {tuple(gate.shape)}, weight {tuple(weight.shape)}, {n_groups} groups")
+    out = torch.empty(y.shape[0], y.shape[1], dtype=out_dtype, device=y.device)
+    status = _lib("recurrent").r2_group_norm_gated(
+        _p(y), _rows(y, "y"), _p(gate), _rows(gate, "gate"), _p(weight), _p(out), _rows(out, "out"), y.shape[0], n_groups,
+        y.shape[1] // n_groups, C.c_float(eps), int(bool(gate_first)), dtype_code(out_dtype), _stream())
+    _check(status, "group_norm_gated")
+    return out
+
+
 class NormedRows:
     """LayerNorm of float32 rows that has not been computed yet: `linear` may compute it inside
     its own kernel (few rows, bfloat16), or `materialize()` runs the LayerNorm kernel. With `beta`
@@ -659,11 +884,14 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                     seq_lens: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
                     window: int = 0, out: torch.Tensor | None = None, *, decode_only: bool = False,
                     max_context: int = 0, q_start: torch.Tensor | None = None, n_tiles: int = 0, v_head_dim: int = 0,
-                    keep_first: int = 0, sink: bool = False, gate: torch.Tensor | None = None) -> torch.Tensor:
+                    keep_first: int = 0, sink: bool = False, gate: torch.Tensor | None = None, softcap: float = 0.0,
+                    sinks: torch.Tensor | None = None, head_gate: torch.Tensor | None = None) -> torch.Tensor:
     """Causal attention of q [T, n_heads * head_dim] over the paged cache -> [T, n_heads * v_head_dim]
     (`v_head_dim` 0: the keys' head size). With a window, `keep_first` keeps a sequence's first keys visible;
     `sink` adds one to the softmax's denominator (an extra exp(0) term: the weights sum to less than one); `gate`
-    [T, n_heads * v_head_dim] multiplies the output by its sigmoid.
+    [T, n_heads * v_head_dim] multiplies the output by its sigmoid. `softcap` > 0 caps the scaled scores at
+    softcap * tanh(s / softcap); `sinks` (float32 [n_heads]) puts exp(sinks[h]) into head h's denominator; `head_gate`
+    (float32 [T, n_heads]) multiplies head h's output by the sigmoid of its entry: these three are the general kernel's.
     `decode_only` says that every row is an entry of its own (one new token each) and
     `max_context` bounds the rows' context lengths; `q_start` (int32 [R + 1]) with `n_tiles`, the
     sum over entries of ceil(rows / 64), lets the tensor-core prefill kernel take the batch. They
@@ -691,7 +919,17 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     group = n_heads // max(n_kv_heads, 1)
     # only the general kernel takes a value head size of its own or a head size that is no multiple of 16; kept
     # first keys, a sink and an output gate are taken by both prefill kernels and the fused decode kernel
-    fits = v_head_dim == head_dim and head_dim % 16 == 0
+    fits = v_head_dim == head_dim and head_dim % 16 == 0 and softcap == 0.0 and sinks is None and head_gate is None
+    head_gate_stride = 0
+    if sinks is not None:
+        _need(sinks, "sinks", torch.float32, 1)
+        if sinks.shape[0] != n_heads:
+            raise KernelError(f"attention: sinks {tuple(sinks.shape)} is not [{n_heads}]")
+    if head_gate is not None:
+        _need(head_gate, "head_gate", torch.float32, 2)
+        if head_gate.shape != (n, n_heads):
+            raise KernelError(f"attention: head_gate {tuple(head_gate.shape)} is not [T, {n_heads}]")
+        head_gate_stride = _rows(head_gate, "head_gate")
     plain = fits and keep_first == 0 and not sink and gate is None
     if plain and q.dtype == torch.bfloat16 and decode_only and _fast_attention and group in (1, 2, 4, 8):
         lib = _lib_for_head_dim("attention_decode", head_dim)
@@ -741,7 +979,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(k_cache), _p(v_cache), C.c_longlong(page_stride),
         page_size, _p(block_tables), block_tables.shape[1], _p(row_entry), _p(positions), _p(seq_lens), n, n_heads,
         n_kv_heads, head_dim, v_head_dim, C.c_float(scale), window, keep_first, int(bool(sink)), _p(gate), gate_stride,
-        n_pages, dtype_code(q.dtype), _stream())
+        n_pages, dtype_code(q.dtype), C.c_float(softcap), _p(sinks), _p(head_gate), head_gate_stride, _stream())
     _check(status, "paged_attention")
     _used("attention_simt")
     return out

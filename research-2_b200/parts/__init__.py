@@ -1,4 +1,4 @@
-from . import attention, block, embedding, mlp, norm, positions  # noqa: F401  (registers the parts)
+from . import attention, block, embedding, mlp, norm, positions, recurrent  # noqa: F401  (registers the parts)
 from .base import (
     LayerSpec, MemberSpec, PartSpec, Runtime, StateSpec, build_part, register_block, register_feed_forward,
     register_mixer, register_norm, register_positions, registry,

@@ -190,3 +190,83 @@ class QKNormAttention:
             self.window, decode_only=ctx.decode_only, max_context=ctx.max_context, q_start=ctx.q_start,
             n_tiles=ctx.n_attention_tiles, v_head_dim=self.v_head_dim, keep_first=self.keep_first, sink=self.sink, gate=gate)
         return ops.linear(mixed, self.w_out, None, w_is_nk=True, residual=residual)
+
+
+@register_mixer("rotary_window_attention")
+class RotaryWindowAttention:
+    """Grouped causal attention over the paged cache with, each chosen by a parameter: a rotation of queries and keys
+    by position, a cap on the scores, a sliding window, a learned sink per head, one output gate per head, and a
+    value head size of its own.
+
+        q, k <- rotate(q, k): of each head the first rot_dims dimensions, dimension i paired with i + rot_dims / 2, by
+                the angle position * rot_base^(-2 i / rot_dims); the other dimensions pass unchanged
+        s = (q . k) * scale, then softcap * tanh(s / softcap)                   (softcap 0: no cap)
+        position p sees the keys (p - window, p]                               (window 0: every key up to p)
+        weights = exp(s) / (sum over seen keys of exp(s) + exp(sink[head]))     (the sink has no key and no value)
+        head's output * sigmoid(w_gate h)[head], then w_out
+
+    params: n_heads, n_kv_heads, head_dim, v_head_dim, scale, softcap, window, rot_dims, rot_base.
+    weights (matrices stored [out, in], no biases): w_q [H * head_dim, D], w_k [G * head_dim, D], w_v [G * v_head_dim, D],
+    w_out [D, H * v_head_dim], and optionally sink [H], w_gate [H, D].
+    Keys are cached after their rotation. Angles, scores, softmax, sink and gate are computed in float32."""
+
+    def __init__(self, params: dict, weights: dict, rt: Runtime):
+        self.n_heads, self.n_kv_heads = int(params["n_heads"]), int(params["n_kv_heads"])
+        self.head_dim, self.v_head_dim = int(params["head_dim"]), int(params["v_head_dim"])
+        self.scale, self.softcap = float(params["scale"]), float(params.get("softcap", 0.0))
+        self.window = int(params.get("window", 0))
+        self.rot_dims, self.rot_base = int(params.get("rot_dims", 0)), float(params.get("rot_base", 1.0))
+        if self.n_heads % self.n_kv_heads != 0:
+            raise ValueError(f"attention: n_heads {self.n_heads} is not a multiple of n_kv_heads {self.n_kv_heads}")
+        if not (1 <= self.head_dim <= 256 and 1 <= self.v_head_dim <= 256):
+            raise ValueError(f"attention: head sizes lie in 1 .. 256, got {self.head_dim} and {self.v_head_dim}")
+        if self.rot_dims % 2 or not 0 <= self.rot_dims <= self.head_dim:
+            raise ValueError(f"attention: {self.rot_dims} rotated dimensions of a head of {self.head_dim}")
+        self.q_width, self.k_width = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim
+        self.v_width, self.o_width = self.n_kv_heads * self.v_head_dim, self.n_heads * self.v_head_dim
+        stacked = [weights["w_q"], weights["w_k"], weights["w_v"]]
+        if [w.shape[0] for w in stacked] != [self.q_width, self.k_width, self.v_width] or weights["w_out"].shape[1] != self.o_width:
+            raise ValueError(f"attention: projections of {[tuple(w.shape) for w in stacked]} and an output of "
+                             f"{tuple(weights['w_out'].shape)} do not fit {self.n_heads} heads, {self.n_kv_heads} kv heads "
+                             f"of {self.head_dim} (values {self.v_head_dim})")
+        self.w_in = matrix(torch.cat(stacked, dim=0), rt)
+        self.w_out = matrix(weights["w_out"], rt)
+        self.sinks = vector(weights["sink"], rt) if weights.get("sink") is not None else None
+        self.w_gate = vector(weights["w_gate"], rt) if weights.get("w_gate") is not None else None   # float32: one gate per head
+        # the rotation's frequencies: exact in float64, then rounded once to float32
+        half = self.rot_dims // 2
+        freq = torch.tensor([self.rot_base ** (-2.0 * i / self.rot_dims) for i in range(half)], dtype=torch.float64)
+        self.inv_freq = freq.to(torch.float32).to(rt.device)
+
+    def matrices(self):
+        return [self.w_in, self.w_out]
+
+    @property
+    def cache_spec(self) -> MemberSpec:
+        return MemberSpec(self.n_kv_heads, self.head_dim, self.window, self.v_head_dim, 0)
+
+    state_spec = None
+    capturable = True
+
+    def _inner(self, h, ctx, cache, writes_cache):
+        proj = ops.linear(h, self.w_in, None, w_is_nk=True)
+        gate = ops.small_linear(h, self.w_gate, None) if self.w_gate is not None else None
+        at = self.q_width + self.k_width
+        q, k, v = proj[:, : self.q_width], proj[:, self.q_width: at], proj[:, at:]
+        if self.rot_dims:
+            ops.rotate_half(proj, self.n_heads + self.n_kv_heads, self.head_dim, self.rot_dims, self.inv_freq, ctx.positions)
+        if writes_cache:
+            ops.kv_write(k, v, cache.k, cache.v, ctx.slot_mapping[cache.group], self.n_kv_heads, self.head_dim,
+                         cache.page_size, cache.page_stride, cache.n_pages, v_head_dim=self.v_head_dim)
+        return ops.paged_attention(
+            q, cache.k, cache.v, cache.page_stride, cache.page_size, cache.n_pages, ctx.block_tables[cache.group],
+            ctx.row_entry, ctx.positions, ctx.seq_lens, self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
+            self.window, decode_only=ctx.decode_only, max_context=ctx.max_context, q_start=ctx.q_start,
+            n_tiles=ctx.n_attention_tiles, v_head_dim=self.v_head_dim, softcap=self.softcap, sinks=self.sinks, head_gate=gate)
+
+    def mix(self, h, ctx, cache=None, state=None, writes_cache: bool = True):
+        """The mixer's output [T, D] in float32, without the residual stream."""
+        return ops.linear(self._inner(h, ctx, cache, writes_cache), self.w_out, None, w_is_nk=True, out_dtype=torch.float32)
+
+    def forward(self, h, residual, ctx, cache, state=None, writes_cache: bool = True):
+        return ops.linear(self._inner(h, ctx, cache, writes_cache), self.w_out, None, w_is_nk=True, residual=residual)

@@ -21,6 +21,8 @@ class PreNormBlock:
     def forward(self, x, ctx, cache=None, state=None, writes_cache: bool = True):
         h = self._normed(self.norm_1, x, self.mixer)
         x = self.mixer.forward(h, x, ctx, cache, state, writes_cache)
+        if self.feed_forward is None:   # a layer without a feed-forward (and without a second norm)
+            return x
         h = self._normed(self.norm_2, x, self.feed_forward)
         return self.feed_forward.forward(h, x, ctx)
 

@@ -71,3 +71,78 @@ class GatedClampedMLP:
         """`gate_up` [T, 2 F]: the input's gate and up projections."""
         y = ops.gated_act(gate_up, self.limit, self.alpha, self.up_offset)
         return ops.linear(y, self.w_down, None, w_is_nk=True, residual=residual)
+
+
+@register_feed_forward("gated_mlp")
+class GatedMLP:
+    """W_down (act(W_gate h) * (W_up h)) with act = relu. params: activation ("relu"). weights: w_gate [F, D], w_up
+    [F, D], w_down [D, F], stored [out, in], no biases. The two input projections run as one product."""
+
+    def __init__(self, params: dict, weights: dict, rt: Runtime):
+        self.activation = params.get("activation", "relu")
+        if self.activation != "relu":
+            raise ValueError(f"gated feed-forward: unknown activation {self.activation!r}")
+        gate, up, down = weights["w_gate"], weights["w_up"], weights["w_down"]
+        if gate.shape != up.shape or down.shape != (gate.shape[1], gate.shape[0]):
+            raise ValueError(f"gated feed-forward: w_gate {tuple(gate.shape)}, w_up {tuple(up.shape)} and w_down {tuple(down.shape)} do not fit")
+        self.w_gate_up = matrix(torch.cat([gate, up], dim=0), rt)
+        self.w_down = matrix(down, rt)
+
+    def matrices(self):
+        return [self.w_gate_up, self.w_down]
+
+    def forward(self, h, residual, ctx):
+        y = ops.expert_act(ops.linear(h, self.w_gate_up, None, w_is_nk=True), self.activation)
+        return ops.linear(y, self.w_down, None, w_is_nk=True, residual=residual)
+
+
+@register_feed_forward("routed_experts")
+class RoutedExperts:
+    """A mixture of small gated feed-forwards, of which each row uses `top`, and optionally one more that every row uses.
+
+        z = W_router h + b_router (float32); the `top` largest logits are chosen (the lower index wins a tie) and their
+        weights are the softmax over the chosen logits only
+        expert: W_down y, y = g sigmoid(alpha g) (u + up_offset), g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit)
+        output = sum over the chosen experts of weight * expert(h) (+ shared(h), same form with shared_limit)
+
+    params: n_experts, top, limit, alpha, up_offset, shared_limit (None: no shared expert).
+    weights: router [E, D], router_b [E], e<i>.w_gate / e<i>.w_up [F, D], e<i>.w_down [D, F] for every expert, and
+    optionally shared.w_gate / shared.w_up [Fs, D], shared.w_down [D, Fs].
+
+    All experts' input projections are stacked into one matrix ([gates of every expert; shared gate; ups of every expert;
+    shared up]) and their down matrices side by side into another, so that a layer is two dense products: the
+    activation between them multiplies an expert's columns by the row's weight for that expert (zero where it was not
+    chosen), and the second product's sum over all columns is the weighted sum over experts. For a few rows
+    (`sparse_rows` or fewer) only the chosen experts' weights are read: a kernel walks each row's choices."""
+
+    sparse_rows = 0   # (the dense form serves every batch until a kernel for the chosen experts alone is there)
+
+    def __init__(self, params: dict, weights: dict, rt: Runtime):
+        self.n_experts, self.top = int(params["n_experts"]), int(params["top"])
+        self.limit, self.alpha, self.up_offset = float(params["limit"]), float(params["alpha"]), float(params["up_offset"])
+        self.shared = params.get("shared_limit") is not None
+        self.shared_limit = float(params["shared_limit"]) if self.shared else self.limit
+        gates = [weights[f"e{i}.w_gate"] for i in range(self.n_experts)]
+        ups = [weights[f"e{i}.w_up"] for i in range(self.n_experts)]
+        downs = [weights[f"e{i}.w_down"] for i in range(self.n_experts)]
+        self.expert_width = gates[0].shape[0]
+        if any(g.shape != gates[0].shape or u.shape != gates[0].shape or d.shape != (g.shape[1], g.shape[0]) for g, u, d in zip(gates, ups, downs)):
+            raise ValueError("routed experts: the experts' matrices differ in shape or do not fit each other")
+        if self.shared:
+            gates.append(weights["shared.w_gate"]); ups.append(weights["shared.w_up"]); downs.append(weights["shared.w_down"])
+        self.w_gate_up = matrix(torch.cat(gates + ups, dim=0), rt)
+        self.w_down = matrix(torch.cat(downs, dim=1), rt)
+        self.router = vector(weights["router"], rt)      # float32: the router is computed in 32-bit
+        self.router_b = vector(weights["router_b"], rt) if weights.get("router_b") is not None else None
+        if self.router.shape[0] != self.n_experts or not 1 <= self.top <= self.n_experts:
+            raise ValueError(f"routed experts: router {tuple(self.router.shape)}, top {self.top}, {self.n_experts} experts")
+
+    def matrices(self):
+        return [self.w_gate_up, self.w_down]
+
+    def forward(self, h, residual, ctx):
+        route, _, _ = ops.route_top_k(h, self.router, self.router_b, self.top)
+        y = ops.expert_act(ops.linear(h, self.w_gate_up, None, w_is_nk=True), "clamped_swish", self.limit, self.alpha,
+                           self.up_offset, route=route, n_experts=self.n_experts, expert_width=self.expert_width,
+                           tail_limit=self.shared_limit)
+        return ops.linear(y, self.w_down, None, w_is_nk=True, residual=residual)

@@ -34,7 +34,8 @@ class LayerNorm:
 @register_norm("rms_norm")
 class RMSNorm:
     """x / sqrt(mean(x^2) + eps) * gain. params: eps; unit_offset (the stored weight is the gain's offset from one:
-    gain = 1 + weight; default false: the weight is the gain). weights: weight."""
+    gain = 1 + weight; default false: the weight is the gain); gain_scale (default 1: a constant factor on the normalised
+    rows, folded into the gain, for instance the factor on a model's logits in its last norm). weights: weight."""
 
     can_be_lazy = True
 
@@ -43,6 +44,8 @@ class RMSNorm:
         self.unit_offset = bool(params.get("unit_offset", False))
         weight = vector(weights["weight"], rt)
         self.gain = weight + 1.0 if self.unit_offset else weight   # in float32, as the kernels would add it
+        if float(params.get("gain_scale", 1.0)) != 1.0:
+            self.gain = self.gain * float(params["gain_scale"])
 
     def forward(self, x, out_dtype, rows=None, lazy: bool = False):
         """Normalised rows in out_dtype. With `lazy` the result is an `ops.NormedRows` that a following
