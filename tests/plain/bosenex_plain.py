@@ -18,8 +18,17 @@ def rms(x, eps):
     return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
 
 
+# A test may set this to a function that disturbs every normalised row on its way into a sublayer (and into the
+# head): how far the logits of a position move under small disturbances says how well-conditioned the position is
+# (a router's close call, a matrix memory whose first q . k is nearly zero).
+DISTURB = None
+# A test may set this to a list: every router then appends, per position, the margin of its choice.
+MARGINS = None
+
+
 def rms_norm(x, w, eps):
-    return rms(x, eps) * w
+    out = rms(x, eps) * w
+    return out if DISTURB is None else DISTURB(out)
 
 
 def lin(w, h):
@@ -28,19 +37,14 @@ def lin(w, h):
 
 
 def soft_cap(x, cap):
-    return cap * torch.tanh(x / cap)
+    return x if not cap else cap * torch.tanh(x / cap)
 
 
 # ---- matrix memory with exponential gates ------------------------------------------------------
-def mlstm(h, w, p, cfg, eps):
-    """w: tensors under '<layer>.mix.' by their last names. cfg: heads, dim, vdim, gate_cap."""
-    H, dk, dv, cap = cfg["heads"], cfg["dim"], cfg["vdim"], float(cfg["gate_cap"])
-    T = h.shape[0]
-    q = lin(w[p + "q"], h).view(T, H, dk) * dk ** -0.5
-    k = lin(w[p + "k"], h).view(T, H, dk)
-    v = lin(w[p + "v"], h).view(T, H, dv)
-    log_i = soft_cap(lin(w[p + "i"], h) + w[p + "i.b"].to(F64), cap)                                   # [T, H]
-    log_f = torch.nn.functional.logsigmoid(soft_cap(lin(w[p + "f"], h) + w[p + "f.b"].to(F64), cap))
+def mlstm_cells(q, k, v, log_i, log_f):
+    """The recurrence alone. q (already scaled), k [T, H, dk], v [T, H, dv], log gates [T, H] -> [T, H, dv]."""
+    T, H, dk = k.shape
+    dv = v.shape[-1]
     S = torch.zeros(H, dk, dv, dtype=F64)
     n = torch.zeros(H, dk, dtype=F64)
     m = torch.zeros(H, dtype=F64)
@@ -55,6 +59,19 @@ def mlstm(h, w, p, cfg, eps):
         num = torch.einsum("hkv,hk->hv", S, q[t])
         den = torch.maximum((n * q[t]).sum(-1).abs(), torch.exp(-m)) + 1e-6
         out[t] = num / den[:, None]
+    return out
+
+
+def mlstm(h, w, p, cfg, eps):
+    """w: tensors under '<layer>.mix.' by their last names. cfg: heads, dim, vdim, gate_cap."""
+    H, dk, dv, cap = cfg["heads"], cfg["dim"], cfg["vdim"], cfg.get("gate_cap")
+    T = h.shape[0]
+    q = lin(w[p + "q"], h).view(T, H, dk) * dk ** -0.5
+    k = lin(w[p + "k"], h).view(T, H, dk)
+    v = lin(w[p + "v"], h).view(T, H, dv)
+    log_i = soft_cap(lin(w[p + "i"], h) + w[p + "i.b"].to(F64), cap)                                   # [T, H]
+    log_f = torch.nn.functional.logsigmoid(soft_cap(lin(w[p + "f"], h) + w[p + "f.b"].to(F64), cap))
+    out = mlstm_cells(q, k, v, log_i, log_f)
     out = rms(out, eps).reshape(T, H * dv) * w[p + "norm"].to(F64)
     out = out * torch.sigmoid(lin(w[p + "g"], h))
     return lin(w[p + "o"], out)
@@ -71,6 +88,33 @@ def rotate(x, positions, dims, base):
     return torch.cat([a * c - b * s, b * c + a * s, x[..., dims:]], dim=-1)
 
 
+def attention_core(q, k, v, scale, softcap, size, sink, first_row=0):
+    """q [R, H, dk]: the queries of the positions first_row .. first_row + R - 1; k [n, G, dk], v [n, G, dv]: the keys and
+    values of the positions 0 .. n - 1. sink [H] or None. -> [R, H, dv]."""
+    R, H, _ = q.shape
+    n, G, dv = v.shape
+    rows = first_row + torch.arange(R)
+    d = rows[:, None] - torch.arange(n)[None, :]
+    seen = d >= 0
+    if size is not None:
+        seen = seen & (d < size)
+    out = torch.zeros(R, H, dv, dtype=F64)
+    for hd in range(H):
+        g = hd // (H // G)
+        s = (q[:, hd] @ k[:, g].T) * scale
+        if softcap:
+            s = soft_cap(s, float(softcap))
+        s = s.masked_fill(~seen, -math.inf)
+        top = s.max(-1, keepdim=True).values
+        extra = 0.0
+        if sink is not None:
+            top = torch.maximum(top, sink[hd])
+            extra = torch.exp(sink[hd] - top)
+        e = torch.exp(s - top)
+        out[:, hd] = (e / (e.sum(-1, keepdim=True) + extra)) @ v[:, g]
+    return out
+
+
 def window_attention(h, w, p, cfg):
     H, G, dk, dv = cfg["heads"], cfg["kv_heads"], cfg["dim"], cfg["vdim"]
     T = h.shape[0]
@@ -82,42 +126,16 @@ def window_attention(h, w, p, cfg):
     if rot is not None:
         q, k = rotate(q, pos, rot["dims"], rot["base"]), rotate(k, pos, rot["dims"], rot["base"])
     size = cfg["mask"]["size"] if cfg.get("mask") else None
-    sink = w[p + "sink"].to(F64)
-    gate = torch.sigmoid(lin(w[p + "g"], h))                                    # [T, H]
-    out = torch.zeros(T, H, dv, dtype=F64)
-    for hd in range(H):
-        g = hd // (H // G)
-        s = (q[:, hd] @ k[:, g].T) * cfg["scale"]
-        if cfg.get("softcap") is not None:
-            s = soft_cap(s, float(cfg["softcap"]))
-        d = pos[:, None] - pos[None, :]
-        seen = d >= 0
-        if size is not None:
-            seen = seen & (d < size)
-        s = s.masked_fill(~seen, -math.inf)
-        top = torch.maximum(s.max(-1, keepdim=True).values, sink[hd])
-        e = torch.exp(s - top)
-        weights = e / (e.sum(-1, keepdim=True) + torch.exp(sink[hd] - top))
-        out[:, hd] = (weights @ v[:, g]) * gate[:, hd: hd + 1]
+    out = attention_core(q, k, v, cfg["scale"], cfg.get("softcap"), size, w[p + "sink"].to(F64))
+    out = out * torch.sigmoid(lin(w[p + "g"], h))[:, :, None]               # one gate per head
     return lin(w[p + "o"], out.reshape(T, H * dv))
 
 
 # ---- state-space mixer with a short convolution -------------------------------------------------
-def ssd(h, w, p, cfg, eps):
-    Hn, dv, N, G, taps, parts = cfg["heads"], cfg["vdim"], cfg["state"], cfg["groups"], cfg["conv"], cfg["norm_groups"]
-    inner, T = Hn * dv, h.shape[0]
-    u = lin(w[p + "in"], h)
-    z, xbc, dt = u[:, :inner], u[:, inner: 2 * inner + 2 * G * N], u[:, 2 * inner + 2 * G * N:]
-    conv, bias = w[p + "conv"].to(F64), w[p + "conv.b"].to(F64)
-    padded = torch.cat([torch.zeros(taps - 1, xbc.shape[1], dtype=F64), xbc])
-    mixed = torch.stack([(padded[t: t + taps].T * conv).sum(-1) for t in range(T)]) + bias
-    mixed = mixed * torch.sigmoid(mixed)
-    x = mixed[:, :inner].view(T, Hn, dv)
-    B = mixed[:, inner: inner + G * N].view(T, G, N)
-    Cm = mixed[:, inner + G * N:].view(T, G, N)
-    dt = torch.nn.functional.softplus(dt + w[p + "dt_bias"].to(F64))            # [T, heads]
-    rate = torch.exp(w[p + "A_log"].to(F64))
-    D = w[p + "D"].to(F64)
+def ssd_cells(x, B, Cm, dt, rate, D):
+    """The recurrence alone. x [T, heads, dv], B and Cm [T, groups, N], dt [T, heads] (after softplus), rate and D [heads]."""
+    T, Hn, dv = x.shape
+    G, N = B.shape[1], B.shape[2]
     S = torch.zeros(Hn, N, dv, dtype=F64)
     y = torch.zeros(T, Hn, dv, dtype=F64)
     group = torch.arange(Hn) // (Hn // G)
@@ -125,6 +143,31 @@ def ssd(h, w, p, cfg, eps):
         decay = torch.exp(-rate * dt[t])
         S = decay[:, None, None] * S + dt[t][:, None, None] * B[t][group][:, :, None] * x[t][:, None, :]
         y[t] = torch.einsum("hnv,hn->hv", S, Cm[t][group]) + D[:, None] * x[t]
+    return y
+
+
+def causal_conv_silu(xbc, conv, bias):
+    """xbc [T, C], conv [C, taps] (the last column is the current token's), zeros before the start."""
+    taps, T = conv.shape[1], xbc.shape[0]
+    padded = torch.cat([torch.zeros(taps - 1, xbc.shape[1], dtype=F64), xbc])
+    mixed = torch.stack([(padded[t: t + taps].T * conv).sum(-1) for t in range(T)]) + bias
+    return mixed * torch.sigmoid(mixed)
+
+
+def ssd(h, w, p, cfg, eps):
+    Hn, dv, N, G, parts = cfg["heads"], cfg["vdim"], cfg["state"], cfg.get("groups", 1), cfg.get("norm_groups", 1)
+    inner, T = Hn * dv, h.shape[0]
+    u = lin(w[p + "in"], h)
+    z, xbc, dt = u[:, :inner], u[:, inner: 2 * inner + 2 * G * N], u[:, 2 * inner + 2 * G * N:]
+    conv, bias = w[p + "conv"].to(F64), w[p + "conv.b"].to(F64)
+    mixed = causal_conv_silu(xbc, conv, bias)
+    x = mixed[:, :inner].view(T, Hn, dv)
+    B = mixed[:, inner: inner + G * N].view(T, G, N)
+    Cm = mixed[:, inner + G * N:].view(T, G, N)
+    dt = torch.nn.functional.softplus(dt + w[p + "dt_bias"].to(F64))            # [T, heads]
+    rate = torch.exp(w[p + "A_log"].to(F64))
+    D = w[p + "D"].to(F64)
+    y = ssd_cells(x, B, Cm, dt, rate, D)
     y = y.reshape(T, inner) * (z * torch.sigmoid(z))
     y = rms(y.view(T, parts, inner // parts), eps).reshape(T, inner) * w[p + "norm"].to(F64)
     return lin(w[p + "o"], y)
@@ -151,6 +194,10 @@ def route(h, w, p, top):
     """-> (chosen experts [T, top], their weights [T, top])."""
     z = lin(w[p + "router"], h) + w[p + "router.b"].to(F64)
     val, idx = torch.topk(z, top, dim=-1)
+    if MARGINS is not None and top < z.shape[1]:
+        # how far the last chosen logit lies above the first one not chosen, in units of |h| |w|
+        ranked = torch.sort(z, dim=-1, descending=True).values
+        MARGINS.append((ranked[:, top - 1] - ranked[:, top]) / (h.norm(dim=-1) * w[p + "router"].to(F64).norm(dim=-1).max()))
     return idx, torch.softmax(val, dim=-1)
 
 
@@ -188,3 +235,22 @@ def forward(config: dict, w: dict, tokens, layers_out: list | None = None):
             layers_out.append(x.clone())
     x = rms_norm(x, w["final.norm"].to(F64), eps)
     return lin(w["head"], x) * config.get("logit_scale", 1.0)
+
+
+def read_model(folder):
+    """(config.json as a dict, tensors by name in float64)."""
+    import json
+    from pathlib import Path
+
+    from safetensors.torch import load_file
+
+    folder = Path(folder)
+    return json.loads((folder / "config.json").read_text()), {n: t.to(F64) for n, t in load_file(str(folder / "model.safetensors")).items()}
+
+
+def generate(config: dict, w: dict, prompt: list[int], n_new: int) -> list[int]:
+    """Greedy continuation, recomputing the whole sequence for every token (first index on ties)."""
+    seq = list(prompt)
+    for _ in range(n_new):
+        seq.append(int(forward(config, w, seq)[-1].argmax()))
+    return seq[len(prompt):]
