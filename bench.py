@@ -19,7 +19,8 @@ A "step" is one decode step. The default run decodes a batch of 8 requests whose
              and 90th-percentile time to a request's first token
   kernels    the step's dominant kernels one by one: microseconds and fraction of the measured peak
 
-`--design zirunex` prints, instead, the same decode and prefill points for Zirunex models with the layer sizes
+`--design bosenex` prints the same points for a Bosenex model beside a Zirunex model of equal layer sizes, and the
+design's kernels one by one. `--design zirunex` prints, instead, the same decode and prefill points for Zirunex models with the layer sizes
 of `--model` beside GPT-2's, and the design's kernels one by one beside their likes.
 
 `--model gpt2-355M` and `--model gpt2-1.5B` run the same at those sizes (the 1.5B decode workload has
@@ -278,6 +279,8 @@ def prefill_point(model, cfg, pk: dict) -> dict:
     if hasattr(cfg, "n_embd"):
         d, f, layers, v = cfg.n_embd, cfg.n_inner, cfg.n_layer, cfg.vocab_size
         flops = 2 * t * layers * (3 * d * d + d * d + 2 * d * f) + layers * n_req * 4 * d * length * (length + 1) / 2 + 2 * n_req * d * v
+    elif hasattr(cfg, "logit_scale"):
+        flops = bosenex_flops(cfg, n_req, length)
     else:
         flops = gated_design_flops(cfg, n_req, length)
     return {"value": t / (ms / 1e3), "tokens": t, "ms": ms, "frac": flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12)}
@@ -376,6 +379,164 @@ def design_points(args, pk: dict) -> dict:
         for name, fn, n_bytes, flops in kernel_cases.gated_cases(8, kv_heads):
             if kv_heads is None or "attention" in name:
                 add(name, fn, n_bytes, flops)
+    out["kernels"] = table
+    return out
+
+
+def bosenex_config(size: str, n_layer: int) -> dict:
+    """A Bosenex configuration with the width, heads, head size, layers and vocabulary of a GPT-2 size: of every three
+    layers two are matrix memories (query/key heads half as wide as value heads) and one is attention (4 query heads a
+    key/value head, window 256, rotation, capped scores) beside a state-space mixer of twice the width (state 64, four
+    taps). The first layer's feed-forward is dense with the gated inner width of the Zirunex configuration beside it;
+    the others route each token to 2 of 8 experts of a quarter of that width and add one expert for every token."""
+    g = SIZES[size]
+    d, h = g["n_embd"], g["n_head"]
+    hd = d // h
+    ff = max(128, round(2 * g["n_inner"] / 3 / 128) * 128)
+    memory = {"heads": h, "dim": hd // 2, "vdim": hd, "gate_cap": 15.0}
+    pair = {"left": {"heads": h, "kv_heads": max(1, h // 4), "dim": hd, "vdim": hd, "scale": hd ** -0.5, "softcap": 30.0,
+                     "mask": {"size": 256}, "rot": {"dims": hd, "base": 10000.0}},
+            "right": {"heads": 2 * h, "vdim": hd, "state": 64, "groups": 1, "conv": 4, "norm_groups": 1}}
+    moe = {"kind": "moe", "router": {"experts": 8, "top": 2}, "expert": {"ff": ff // 4, "limit": 7.0}, "shared": {"ff": ff // 4, "limit": 7.0}}
+    layers = [{"type": "parallel" if i % 3 == 2 else "mlstm", "mixer": pair if i % 3 == 2 else memory,
+               "mlp": {"kind": "dense", "ff": ff} if i == 0 else moe} for i in range(n_layer)]
+    return {"architecture": "Bosenex", "vocab": g["vocab_size"], "width": d, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "logit_scale": 1.0, "layers": layers}
+
+
+def bosenex_flops(cfg, n_req: int, length: int) -> float:
+    """Flops that one prefill step of n_req prompts of `length` tokens NEEDS in a Bosenex configuration: products with
+    the weights a token uses (its chosen experts, not all), the recurrences, and the attention's seen pairs."""
+    from research_2_b200.config.bosenex import DenseMlp, MatrixMemoryMixer
+
+    t, d, total = n_req * length, cfg.width, 0.0
+    for layer in cfg.layers:
+        m = layer.mixer
+        if isinstance(m, MatrixMemoryMixer):
+            qk, v = m.heads * m.dim, m.heads * m.vdim
+            total += 2 * t * d * (2 * qk + 2 * v) + 2 * t * v * d + t * m.heads * 6 * m.dim * m.vdim
+        else:
+            a, s = m.left, m.right
+            q, kv, o = a.heads * a.dim, a.kv_heads * (a.dim + a.vdim), a.heads * a.vdim
+            total += 2 * t * d * (q + kv) + 2 * t * o * d
+            total += n_req * 2 * (q + o) * sum(min(i + 1, a.window or length) for i in range(length))
+            inner = s.heads * s.vdim
+            total += 2 * t * d * (2 * inner + 2 * s.groups * s.state + s.heads) + 2 * t * inner * d + t * s.heads * 4 * s.state * s.vdim
+        if isinstance(layer.mlp, DenseMlp):
+            total += 2 * t * d * 3 * layer.mlp.ff
+        elif layer.mlp is not None:
+            total += 2 * t * d * 3 * (layer.mlp.top * layer.mlp.ff + layer.mlp.shared_ff)
+    return total + 2 * n_req * d * cfg.vocab_size
+
+
+def bosenex_points(args, pk: dict) -> dict:
+    """`--design bosenex`: prefill and decode throughput of a Bosenex model with the layer sizes of `--model`, beside a
+    Zirunex model of that size (the closest of the other models: grouped attention with a window, gated feed-forward)
+    through the same loops, and the design's kernels one by one beside their likes."""
+    import torch
+    from research_2_b200.kernels import ops
+    from research_2_b200.profiling import kernel_cases
+
+    g = SIZES[args.model]
+    d, h = g["n_embd"], g["n_head"]
+    hd = d // h
+    variants = {
+        "zirunex, 4 query heads a kv head, window 256": gated_design_config(args.model, args.layers, max(1, h // 4), 256, 0),
+        "bosenex": bosenex_config(args.model, args.layers),
+    }
+    out = {"design": "bosenex", "sizes_of": args.model, "layers": args.layers, "prompt_len": PROMPT_LEN, "models": {}}
+    for name, data in variants.items():
+        model, cfg = build_gated_design(data)
+        point = {}
+        for batch in (8, 64):
+            steps = min(args.steps, 96)
+            value, ms, loop, kv_bytes = decode_point(model, batch, steps, args.warmup)
+            state_bytes = 2 * batch * sum(4 * int(torch.tensor(spec.shape).prod()) for spec in model.state_members)   # read and written
+            achieved = (model.weight_bytes_per_step() + kv_bytes + state_bytes) / (ms / 1e3) / 1e9
+            point[f"decode_b{batch}"] = {"tokens/s": round(value), "ms_per_step": round(ms, 4), "kernels_per_step": loop.graph.kernels,
+                                         "hbm_frac": round(achieved / pk["hbm_gbs"], 3)}
+            del loop
+            torch.cuda.empty_cache()
+        pre = prefill_point(model, cfg, pk)
+        point["prefill_2x1024"] = {"tokens/s": round(pre["value"]), "ms": round(pre["ms"], 3), "bf16_frac": round(pre["frac"], 3)}
+        out["models"][name] = point
+        del model
+        torch.cuda.empty_cache()
+
+    # the design's kernels one by one, at a prompt step (2 x 1,024 rows) and a decode step (8 rows)
+    table = {}
+
+    def add(name, fn, n_bytes=0, flops=0):
+        us = kernel_cases.time_in_graph(fn)
+        entry = {"us": round(us, 2)}
+        if n_bytes:
+            entry.update(frac=round(n_bytes / us / 1e3 / pk["hbm_gbs"], 3), of="copy bandwidth")
+        elif flops:
+            entry.update(frac=round(flops / us / 1e6 / pk["bf16_tflops"], 3), of="bf16 peak")
+        table[name] = entry
+
+    dev, bf = "cuda:0", torch.bfloat16
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)  # noqa: E731
+    ff = max(128, round(2 * g["n_inner"] / 3 / 128) * 128)
+    for label, n_entries, rows_each in (("2 x 1,024 rows", 2, 1024), ("8 decoded rows", 8, 1)):
+        t = n_entries * rows_each
+        q_start = i32([i * rows_each for i in range(n_entries + 1)])
+        slots, fresh = i32(list(range(n_entries))), i32([0] * n_entries)
+        row_entry = i32([e for e in range(n_entries) for _ in range(rows_each)])
+        x32 = torch.randn(t, d, device=dev)
+        hrow = torch.randn(t, d, device=dev).to(bf)
+        gain = torch.ones(d, device=dev)
+        add(f"stream norm (rms), {label}", lambda: ops.rms_norm(x32, gain, 1e-5, bf), n_bytes=t * d * 6)
+        # matrix memory
+        dk = hd // 2
+        proj = torch.randn(t, 2 * h * dk + 2 * d, device=dev).to(bf)
+        gates = torch.randn(t, 2 * h, device=dev)
+        state = torch.zeros(n_entries, h * ops.mlstm_state_floats(dk, hd), device=dev)
+        w_gates = torch.randn(2 * h, d, device=dev) * 0.02
+        scan_bytes = t * (2 * h * dk + d) * 2 + t * d * 4 + 2 * state.numel() * 4
+        add(f"matrix memory: recurrence, {h} heads of {dk} x {hd}, {label}",
+            lambda: ops.mlstm_scan(proj[:, : h * dk], proj[:, h * dk: 2 * h * dk], proj[:, 2 * h * dk: 2 * h * dk + d], gates, 15.0, dk ** -0.5,
+                                   state, q_start, slots, fresh, h, dk, hd), n_bytes=scan_bytes)
+        o32 = torch.randn(t, d, device=dev)
+        add(f"matrix memory: heads' norm and gate, {label}", lambda: ops.group_norm_gated(o32, proj[:, 2 * h * dk + d:], gain, h, 1e-5, False, bf),
+            n_bytes=t * d * 8)
+        add(f"gates in 32-bit ({2 * h} outputs), {label}", lambda: ops.small_linear(hrow, w_gates, None), n_bytes=t * d * 2 + w_gates.numel() * 4)
+        # state space
+        sh, n_state, taps = 2 * h, 64, 4
+        inner, channels = sh * hd, sh * hd + 2 * n_state
+        xbc = torch.randn(t, channels, device=dev).to(bf)
+        conv_w, conv_b = torch.randn(channels, taps, device=dev) * 0.3, torch.zeros(channels, device=dev)
+        off = sh * n_state * hd
+        sstate = torch.zeros(n_entries, off + (taps - 1) * channels, device=dev)
+        steps_in = torch.randn(t, sh, device=dev)
+        per_head = torch.zeros(sh, device=dev)
+        add(f"state space: convolution + silu, {channels:,} channels, {label}",
+            lambda: ops.causal_conv(xbc, conv_w, conv_b, sstate, off, row_entry, q_start, slots, fresh), n_bytes=t * channels * 4)
+        add(f"state space: recurrence, {sh} heads of {n_state} x {hd}, {label}",
+            lambda: ops.ssd_scan(xbc[:, :inner], xbc[:, inner: inner + n_state], xbc[:, inner + n_state:], steps_in, per_head, per_head, per_head,
+                                 sstate, q_start, slots, fresh, sh, 1, n_state, hd, conv_in=xbc, conv_taps=taps, conv_state_off=off),
+            n_bytes=t * channels * 2 + t * inner * 4 + 2 * sstate.numel() * 4)
+        y32, z = torch.randn(t, inner, device=dev), torch.randn(t, inner, device=dev).to(bf)
+        gain2 = torch.ones(inner, device=dev)
+        add(f"state space: gate and norm, {label}", lambda: ops.group_norm_gated(y32, z, gain2, 1, 1e-5, True, bf), n_bytes=t * inner * 8)
+        a32, b32 = torch.randn(t, d, device=dev), torch.randn(t, d, device=dev)
+        add(f"two mixers join the stream, {label}", lambda: ops.pair_norm_add(x32, a32, b32, gain, gain, 1e-5), n_bytes=t * d * 16)
+        # attention beside it
+        kvh = max(1, h // 4)
+        qkv = torch.randn(t, (h + 2 * kvh) * hd, device=dev).to(bf)
+        inv_freq = torch.tensor([10000.0 ** (-2.0 * i / hd) for i in range(hd // 2)], device=dev)
+        positions = i32([1023 if rows_each == 1 else p for _ in range(n_entries) for p in range(rows_each)])
+        add(f"rotation of {h + kvh} heads of {hd}, {label}", lambda: ops.rotate_half(qkv, h + kvh, hd, hd, inv_freq, positions), n_bytes=t * (h + kvh) * hd * 4)
+        # experts
+        gu = torch.randn(t, 2 * (8 * (ff // 4) + ff // 4), device=dev).to(bf)
+        router = torch.randn(8, d, device=dev) * 0.02
+        route, _, _ = ops.route_top_k(hrow, router, None, 2)
+        add(f"router: 8 logits in 32-bit, top 2, softmax, {label}", lambda: ops.route_top_k(hrow, router, None, 2), n_bytes=t * d * 2)
+        add(f"experts' gated unit with routing weights, {gu.shape[1] // 2:,} columns, {label}",
+            lambda: ops.expert_act(gu, "clamped_swish", 7.0, 1.702, 1.0, route=route, n_experts=8, expert_width=ff // 4, tail_limit=7.0),
+            n_bytes=t * gu.shape[1] * 3)
+        gu_like = torch.randn(t, 2 * ff, device=dev).to(bf)
+        add(f"its like: gated unit of {ff:,} columns (Zirunex), {label}", lambda: ops.gated_act(gu_like, 7.0, 1.702, 1.0), n_bytes=t * ff * 6)
     out["kernels"] = table
     return out
 
@@ -553,7 +714,7 @@ def main() -> int:
     ap.add_argument("--phases", action="store_true", help="print where a layer's time goes inside the resident decode kernel at --batch rows, and stop")
     ap.add_argument("--logits-ctas", action="store_true", help="print when each CTA of a decode step's logits product starts and ends (its waves), and stop")
     ap.add_argument("--prefill", action="store_true", help="print the prefill point (2 x 1,024 tokens in one step) alone, and stop")
-    ap.add_argument("--design", default=None, choices=("zirunex",),
+    ap.add_argument("--design", default=None, choices=("zirunex", "bosenex"),
                     help="print prefill and decode throughput of that design at the layer sizes of --model beside GPT-2's, "
                          "and its kernels beside their likes, and stop (the default workload is GPT-2's)")
     args = ap.parse_args()
@@ -588,7 +749,7 @@ def main() -> int:
 
     pk, pk_source = peaks()
     if args.design:
-        print(json.dumps(design_points(args, pk)))
+        print(json.dumps(bosenex_points(args, pk) if args.design == "bosenex" else design_points(args, pk)))
         return 0
     model, cfg = build_model(args.layers, size=args.model)
     if args.phases:

@@ -44,6 +44,10 @@ struct DecodeParams {
   // [rows, n_heads * HD]) multiplies the output by its sigmoid. `split_p` carries the softmax's weights
   // into the second product as the sum of two bfloat16 numbers instead of one rounded one.
   int keep_first; int sink; const bf16* gate; int gate_row_stride; int split_p;
+  // `softcap` > 0 caps the scaled scores at softcap * tanh(s / softcap); `sinks` (may be null; [n_heads]) puts
+  // exp(sinks[h]) instead of exp(0) into head h's denominator; `head_gate` (may be null; float [rows, n_heads])
+  // multiplies head h's output by the sigmoid of its entry.
+  float softcap; const float* sinks; const float* head_gate; int head_gate_stride;
   int n_slices;
   float* part_o;   // [rows, n_heads, n_slices, HD]
   float* part_ml;  // [rows, n_heads, n_slices, 2]
@@ -81,11 +85,17 @@ __device__ __forceinline__ uint32_t pack_rest(float lo, float hi, uint32_t packe
 }
 // The end of a row's softmax: with a sink the denominator counts one more key of score 0; with a gate the
 // output is multiplied by the sigmoid of the gate's value.
-__device__ __forceinline__ float finish(float o, float l, float mx, int sink, const bf16* gate) {
-  if (sink) l += mx > -INFINITY ? __expf(-mx) : 1.f;
+__device__ __forceinline__ float finish(float o, float l, float mx, int sink, const bf16* gate, float sink_value = 0.f,
+                                        const float* head_gate = nullptr) {
+  if (sink) l += mx > -INFINITY ? __expf(sink_value - mx) : 1.f;   // (no key seen: o is zero whatever l is)
   float y = l > 0.f ? o / l : 0.f;
   if (gate != nullptr) y *= 1.f / (1.f + __expf(-__bfloat162float(*gate)));
+  if (head_gate != nullptr) y *= 1.f / (1.f + __expf(-*head_gate));
   return y;
+}
+// cap * tanh(s / cap) by one exponential: tanh(x) = 1 - 2 / (exp(2 x) + 1)
+__device__ __forceinline__ float soft_cap(float s, float cap) {
+  return cap * (1.f - __fdividef(2.f, __expf(2.f * s / cap) + 1.f));
 }
 
 constexpr bool MMA_FITS = HD <= 128;   // the tensor-core form keeps HD / 2 output floats per lane
@@ -282,6 +292,10 @@ decode_kernel(const DecodeParams p) {
           const bool seen = v0 + nt * 8 + 2 * tq + c < n_keys;
           sc[nt][c] = seen ? sc[nt][c] * p.scale : -INFINITY;
           sc[nt][2 + c] = seen ? sc[nt][2 + c] * p.scale : -INFINITY;
+          if (X && p.softcap > 0.f) {
+            if (seen) sc[nt][c] = soft_cap(sc[nt][c], p.softcap);
+            if (seen) sc[nt][2 + c] = soft_cap(sc[nt][2 + c], p.softcap);
+          }
           mx_a = fmaxf(mx_a, sc[nt][c]);
           mx_b = fmaxf(mx_b, sc[nt][2 + c]);
         }
@@ -375,6 +389,7 @@ decode_kernel(const DecodeParams p) {
 #pragma unroll
     for (int g = 0; g < G; ++g) {
       float sv = valid ? s[g] : -INFINITY;
+      if (X && p.softcap > 0.f && valid) sv = soft_cap(sv, p.softcap);
       float m_new = fmaxf(m[g], warp_max(sv));
       float corr = __expf(m[g] - m_new);
       pr[g] = valid ? __expf(sv - m_new) : 0.f;
@@ -465,7 +480,9 @@ decode_kernel(const DecodeParams p) {
     }
     if (p.n_slices == 1) {
       const bf16* gate = (X && p.gate != nullptr) ? p.gate + size_t(t) * p.gate_row_stride + size_t(h0 + g) * HD + d : nullptr;
-      p.out[size_t(t) * p.out_row_stride + size_t(h0 + g) * HD + d] = __float2bfloat16_rn(finish(o, lsum, mx, X ? p.sink : 0, gate));
+      p.out[size_t(t) * p.out_row_stride + size_t(h0 + g) * HD + d] = __float2bfloat16_rn(finish(
+          o, lsum, mx, X ? p.sink : 0, gate, (X && p.sinks != nullptr) ? p.sinks[h0 + g] : 0.f,
+          (X && p.head_gate != nullptr) ? p.head_gate + size_t(t) * p.head_gate_stride + h0 + g : nullptr));
     } else {
       size_t at = (size_t(t) * p.n_heads + h0 + g) * p.n_slices + slice;
       p.part_o[at * HD + d] = o;
@@ -502,7 +519,9 @@ decode_kernel(const DecodeParams p) {
           }
         }
         const bf16* gate = (X && p.gate != nullptr) ? p.gate + size_t(t) * p.gate_row_stride + size_t(h0 + g) * HD + d : nullptr;
-        p.out[size_t(t) * p.out_row_stride + size_t(h0 + g) * HD + d] = __float2bfloat16_rn(finish(o, lsum, mx, X ? p.sink : 0, gate));
+        p.out[size_t(t) * p.out_row_stride + size_t(h0 + g) * HD + d] = __float2bfloat16_rn(finish(
+          o, lsum, mx, X ? p.sink : 0, gate, (X && p.sinks != nullptr) ? p.sinks[h0 + g] : 0.f,
+          (X && p.head_gate != nullptr) ? p.head_gate + size_t(t) * p.head_gate_stride + h0 + g : nullptr));
       }
     }
   }
@@ -511,7 +530,8 @@ decode_kernel(const DecodeParams p) {
 // out[t, h, :] = sum_s exp(m_s - m) o_s / sum_s exp(m_s - m) l_s, slices in order.
 __global__ void merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out,
                              int out_row_stride, int n_heads, int n_slices, int sink, const bf16* __restrict__ gate,
-                             int gate_row_stride) {
+                             int gate_row_stride, const float* __restrict__ sinks, const float* __restrict__ head_gate,
+                             int head_gate_stride) {
   pdl_launch_dependents();  // the next kernel may begin its prologue
   pdl_wait();               // the previous kernel's writes are visible from here on
   const int t = blockIdx.y, h = blockIdx.x;
@@ -528,7 +548,8 @@ __global__ void merge_kernel(const float* __restrict__ part_o, const float* __re
       }
     }
     const bf16* gp = gate != nullptr ? gate + size_t(t) * gate_row_stride + size_t(h) * HD + d : nullptr;
-    out[size_t(t) * out_row_stride + size_t(h) * HD + d] = __float2bfloat16_rn(finish(o, l, mx, sink, gp));
+    out[size_t(t) * out_row_stride + size_t(h) * HD + d] = __float2bfloat16_rn(finish(
+        o, l, mx, sink, gp, sinks != nullptr ? sinks[h] : 0.f, head_gate != nullptr ? head_gate + size_t(t) * head_gate_stride + h : nullptr));
   }
 }
 
@@ -594,6 +615,7 @@ extern "C" int r2_attention_decode(const void* q, int q_row_stride, void* out, i
   p.n_heads = n_heads; p.n_kv_heads = n_kv_heads;
   p.scale = scale; p.window = window; p.n_slices = n_slices;
   p.keep_first = 0; p.sink = 0; p.gate = nullptr; p.gate_row_stride = 0; p.split_p = 0;
+  p.softcap = 0.f; p.sinks = nullptr; p.head_gate = nullptr; p.head_gate_stride = 0;
   p.part_o = scratch;
   p.part_ml = scratch != nullptr ? scratch + (long long)n_rows * n_heads * n_slices * HD : nullptr;
   p.k_new = nullptr; p.v_new = nullptr; p.new_row_stride = 0; p.slot_mapping = nullptr;
@@ -608,7 +630,7 @@ extern "C" int r2_attention_decode(const void* q, int q_row_stride, void* out, i
   }
   if (status != R2_OK || n_slices == 1) return status;
   r2_launch(merge_kernel, dim3(dim3(n_heads, n_rows)), dim3(HD >= 128 ? 128 : 64), size_t(0), stream, p.part_o, p.part_ml, (bf16*)out, out_row_stride, n_heads, n_slices, p.sink,
-            p.gate, p.gate_row_stride);
+            p.gate, p.gate_row_stride, p.sinks, p.head_gate, p.head_gate_stride);
   return launch_status();
 }
 
@@ -617,7 +639,8 @@ namespace {
 // The plain form for groups of 1, 2, 4 and 8 query heads; the form with extras for every group up to 8.
 template <int G>
 int launch_fused(const DecodeParams& p, int n_rows, cudaStream_t stream) {
-  const bool extras = p.keep_first > 0 || p.sink != 0 || p.gate != nullptr || p.split_p != 0;
+  const bool extras = p.keep_first > 0 || p.sink != 0 || p.gate != nullptr || p.split_p != 0 || p.softcap > 0.f ||
+                      p.sinks != nullptr || p.head_gate != nullptr;
   if constexpr (G == 1 || G == 2 || G == 4 || G == 8) {
     if (!extras) return launch<G, false>(p, n_rows, stream);
   }
@@ -632,7 +655,7 @@ int launch_fused(const DecodeParams& p, int n_rows, cudaStream_t stream) {
 // finishes last, so there is neither a separate cache-write kernel nor a merge kernel.
 // `scratch` as for r2_attention_decode; `counters` holds n_rows * n_kv_heads ints that are
 // zero before the call and zero again after it. `keep_first`, `sink`, `gate` and `split_p`: see DecodeParams.
-extern "C" int r2_attention_decode_fused(const void* q, int q_row_stride, void* out, int out_row_stride, void* k_cache,
+extern "C" int r2_attention_decode_fused_capped(const void* q, int q_row_stride, void* out, int out_row_stride, void* k_cache,
                                          void* v_cache, long long page_stride, int page_size, int n_pages,
                                          const int32_t* block_tables, int table_width, const int32_t* row_entry,
                                          const int32_t* positions, const int32_t* seq_lens, int n_rows, int n_heads,
@@ -640,6 +663,7 @@ extern "C" int r2_attention_decode_fused(const void* q, int q_row_stride, void* 
                                          const void* v_new, int new_row_stride, const int32_t* slot_mapping,
                                          float* scratch, long long scratch_floats, int* counters, int n_counters,
                                          int keep_first, int sink, const void* gate, int gate_row_stride, int split_p,
+                                         float softcap, const float* sinks, const float* head_gate, int head_gate_stride,
                                          cudaStream_t stream) {
   if (n_rows <= 0) return R2_OK;
   if (keep_first < 0) return R2_BAD_SHAPE;
@@ -658,7 +682,8 @@ extern "C" int r2_attention_decode_fused(const void* q, int q_row_stride, void* 
   p.row_entry = row_entry; p.positions = positions; p.seq_lens = seq_lens;
   p.n_heads = n_heads; p.n_kv_heads = n_kv_heads;
   p.scale = scale; p.window = window; p.n_slices = n_slices;
-  p.keep_first = keep_first; p.sink = sink; p.gate = (const bf16*)gate; p.gate_row_stride = gate_row_stride; p.split_p = split_p;
+  p.keep_first = keep_first; p.sink = (sink || sinks != nullptr) ? 1 : 0; p.gate = (const bf16*)gate; p.gate_row_stride = gate_row_stride; p.split_p = split_p;
+  p.softcap = softcap; p.sinks = sinks; p.head_gate = head_gate; p.head_gate_stride = head_gate_stride;
   p.part_o = scratch;
   p.part_ml = scratch != nullptr ? scratch + (long long)n_rows * n_heads * n_slices * HD : nullptr;
   p.k_new = (const bf16*)k_new; p.v_new = (const bf16*)v_new; p.new_row_stride = new_row_stride;
@@ -676,6 +701,21 @@ extern "C" int r2_attention_decode_fused(const void* q, int q_row_stride, void* 
     case 8: return launch_fused<8>(p, n_rows, stream);
     default: return R2_UNSUPPORTED;
   }
+}
+
+extern "C" int r2_attention_decode_fused(const void* q, int q_row_stride, void* out, int out_row_stride, void* k_cache,
+                                         void* v_cache, long long page_stride, int page_size, int n_pages,
+                                         const int32_t* block_tables, int table_width, const int32_t* row_entry,
+                                         const int32_t* positions, const int32_t* seq_lens, int n_rows, int n_heads,
+                                         int n_kv_heads, float scale, int window, int n_slices, const void* k_new,
+                                         const void* v_new, int new_row_stride, const int32_t* slot_mapping,
+                                         float* scratch, long long scratch_floats, int* counters, int n_counters,
+                                         int keep_first, int sink, const void* gate, int gate_row_stride, int split_p,
+                                         cudaStream_t stream) {
+  return r2_attention_decode_fused_capped(q, q_row_stride, out, out_row_stride, k_cache, v_cache, page_stride, page_size, n_pages,
+                                          block_tables, table_width, row_entry, positions, seq_lens, n_rows, n_heads, n_kv_heads, scale,
+                                          window, n_slices, k_new, v_new, new_row_stride, slot_mapping, scratch, scratch_floats, counters,
+                                          n_counters, keep_first, sink, gate, gate_row_stride, split_p, 0.f, nullptr, nullptr, 0, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -58,6 +58,10 @@ struct PrefillParams {
   // [rows, n_heads * HD]) multiplies the output by its sigmoid. `split_p` carries the softmax's weights
   // into the second product as the sum of two bfloat16 numbers instead of one rounded one.
   int keep_first; int sink; const bf16* gate; int gate_row_stride; int split_p;
+  // `softcap` > 0 caps the scaled scores at softcap * tanh(s / softcap); `sinks` (may be null; [n_heads]) puts
+  // exp(sinks[h]) instead of exp(0) into head h's denominator; `head_gate` (may be null; float [rows, n_heads])
+  // multiplies head h's output by the sigmoid of its entry.
+  float softcap; const float* sinks; const float* head_gate; int head_gate_stride;
   int box_rows;      // TMA form: key rows per tensor copy (the page size, or 64 for larger pages)
   int* error_flag;   // TMA form: where a bounded wait that ran out is recorded
 };
@@ -347,6 +351,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
       // scale, mask, online softmax: rows row_a (c0, c1) and row_b (c2, c3). Scores are kept in
       // units of log2(e) so that one exp2 per element does the softmax's exponential.
       const float scale2 = p.scale * 1.4426950408889634f;
+      if (p.softcap > 0.f) {
+        // capped scores, handed on in the raw scores' units (divided by the scale again): tanh(x) = 1 - 2 / (exp(2 x) + 1)
+        const float in = 2.f * p.scale / p.softcap, back = p.softcap / p.scale;
+#pragma unroll
+        for (int nt = 0; nt < BN / 8; ++nt) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) s[nt][c] = back * (1.f - __fdividef(2.f, __expf(s[nt][c] * in) + 1.f));
+        }
+      }
       float mx_a = -INFINITY, mx_b = -INFINITY;
       // every key of this tile is visible to every row of this warp: no mask to evaluate
       const int warp_pmin = pmin + warp * 16, warp_pmax = pmin + min(warp * 16 + 15, rows_here - 1);
@@ -450,11 +463,16 @@ prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant_
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
 
-  if (p.sink) {  // one more key of score 0 in every denominator (running maxima are in units of log2 e)
-    l_run[0] += m_run[0] > -INFINITY ? fast_exp2(-m_run[0]) : 1.f;
-    l_run[1] += m_run[1] > -INFINITY ? fast_exp2(-m_run[1]) : 1.f;
+  if (p.sink) {  // one more key of score 0 (or sinks[h]) in every denominator (running maxima are in units of log2 e)
+    const float sv = p.sinks != nullptr ? p.sinks[h] * 1.4426950408889634f : 0.f;
+    l_run[0] += m_run[0] > -INFINITY ? fast_exp2(sv - m_run[0]) : 1.f;
+    l_run[1] += m_run[1] > -INFINITY ? fast_exp2(sv - m_run[1]) : 1.f;
   }
-  const float inv_a = l_run[0] > 0.f ? 1.f / l_run[0] : 0.f, inv_b = l_run[1] > 0.f ? 1.f / l_run[1] : 0.f;
+  float inv_a = l_run[0] > 0.f ? 1.f / l_run[0] : 0.f, inv_b = l_run[1] > 0.f ? 1.f / l_run[1] : 0.f;
+  if (p.head_gate != nullptr) {  // one gate per head
+    if (row_a < rows_here) inv_a *= 1.f / (1.f + __expf(-p.head_gate[size_t(t0 + r0 + row_a) * p.head_gate_stride + h]));
+    if (row_b < rows_here) inv_b *= 1.f / (1.f + __expf(-p.head_gate[size_t(t0 + r0 + row_b) * p.head_gate_stride + h]));
+  }
 #pragma unroll
   for (int dt = 0; dt < DTILES; ++dt) {
     int d = dt * 8 + 2 * tq;
@@ -507,12 +525,13 @@ int launch(const CUtensorMap& mk, const CUtensorMap& mv, const PrefillParams& p,
 // harmless: the CTAs beyond find no tile). error_flag: a device word in which a bounded wait that
 // ran out is recorded (may be null; the tensor-copy form is then not used). `keep_first`, `sink`, `gate`
 // and `split_p`: see PrefillParams.
-extern "C" int r2_attention_prefill(const void* q, int q_row_stride, void* out, int out_row_stride, const void* k_cache,
+extern "C" int r2_attention_prefill_capped(const void* q, int q_row_stride, void* out, int out_row_stride, const void* k_cache,
                                     const void* v_cache, long long page_stride, int page_size, int n_pages,
                                     const int32_t* block_tables, int table_width, const int32_t* q_start,
                                     const int32_t* seq_lens, int n_entries, int n_tiles, int n_heads, int n_kv_heads,
                                     float scale, int window, int* error_flag, int keep_first, int sink, const void* gate,
-                                    int gate_row_stride, int split_p, cudaStream_t stream) {
+                                    int gate_row_stride, int split_p, float softcap, const float* sinks, const float* head_gate,
+                                    int head_gate_stride, cudaStream_t stream) {
   if (n_entries <= 0 || n_tiles <= 0) return R2_OK;
   if (n_heads < 1 || n_kv_heads < 1 || n_heads % n_kv_heads != 0 || page_size < 1 || window < 0 || keep_first < 0) return R2_BAD_SHAPE;
   if (gate != nullptr && (gate_row_stride % 2 != 0 || (reinterpret_cast<uintptr_t>(gate) & 3))) return R2_BAD_ALIGN;
@@ -530,7 +549,8 @@ extern "C" int r2_attention_prefill(const void* q, int q_row_stride, void* out, 
   p.q_start = q_start; p.seq_lens = seq_lens; p.n_entries = n_entries;
   p.n_heads = n_heads; p.n_kv_heads = n_kv_heads;
   p.scale = scale; p.window = window;
-  p.keep_first = keep_first; p.sink = sink; p.gate = (const bf16*)gate; p.gate_row_stride = gate_row_stride; p.split_p = split_p;
+  p.keep_first = keep_first; p.sink = (sink || sinks != nullptr) ? 1 : 0; p.gate = (const bf16*)gate; p.gate_row_stride = gate_row_stride; p.split_p = split_p;
+  p.softcap = softcap; p.sinks = sinks; p.head_gate = head_gate; p.head_gate_stride = head_gate_stride;
   p.box_rows = 0;
   p.error_flag = error_flag;
   CUtensorMap mk, mv;
@@ -546,6 +566,17 @@ extern "C" int r2_attention_prefill(const void* q, int q_row_stride, void* out, 
   memset(&mk, 0, sizeof(mk));
   memset(&mv, 0, sizeof(mv));
   return launch<false>(mk, mv, p, n_tiles, stream);
+}
+
+extern "C" int r2_attention_prefill(const void* q, int q_row_stride, void* out, int out_row_stride, const void* k_cache,
+                                    const void* v_cache, long long page_stride, int page_size, int n_pages,
+                                    const int32_t* block_tables, int table_width, const int32_t* q_start,
+                                    const int32_t* seq_lens, int n_entries, int n_tiles, int n_heads, int n_kv_heads,
+                                    float scale, int window, int* error_flag, int keep_first, int sink, const void* gate,
+                                    int gate_row_stride, int split_p, cudaStream_t stream) {
+  return r2_attention_prefill_capped(q, q_row_stride, out, out_row_stride, k_cache, v_cache, page_stride, page_size, n_pages, block_tables,
+                                     table_width, q_start, seq_lens, n_entries, n_tiles, n_heads, n_kv_heads, scale, window, error_flag,
+                                     keep_first, sink, gate, gate_row_stride, split_p, 0.f, nullptr, nullptr, 0, stream);
 }
 
 // Tests and measurements compare the two ways of bringing the tiles in.

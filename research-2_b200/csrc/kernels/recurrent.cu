@@ -22,7 +22,8 @@
 
 namespace {
 
-constexpr int TILE = 8;  // rows whose vectors are staged at a time
+constexpr int TILE = 16;       // rows whose vectors are staged at a time
+constexpr int NORM_COPIES = 8;  // copies of a matrix memory's normaliser and maximum: one per slice of the columns at most
 
 constexpr int MODE_MLSTM = 0, MODE_SSD = 1;
 
@@ -41,8 +42,7 @@ struct ScanArgs {
   const float* skip;                     // state space, per head: y += skip * v
   float cap;                             // mLSTM: gates are cap * tanh(x / cap); 0 = no cap
   float read_scale;                      // r is multiplied by it
-  float* state; long long slot_stride;   // per request slot; per head: S [rows][cols] (+ mLSTM: n [rows] and m, once per
-                                         // slice of the columns: every CTA reads and renews a copy of its own)
+  float* state; long long slot_stride;   // per request slot; per head: S [rows][cols] (+ mLSTM: NORM_COPIES times n [rows], m)
   int head_stride;
   const int32_t* q_start; const int32_t* state_slot; const int32_t* fresh;
   float* out; int out_stride;            // [T, heads * cols] float
@@ -56,7 +56,7 @@ __global__ void __launch_bounds__(256)
 outer_scan_kernel(const ScanArgs a) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   const int e = blockIdx.x, h = blockIdx.y;
   const int row0 = a.q_start[e], row1 = a.q_start[e + 1];
   if (row1 <= row0) return;  // an entry without rows touches no slot
@@ -65,13 +65,17 @@ outer_scan_kernel(const ScanArgs a) {
   float* rs = smem;                       // [TILE][padded]
   float* ws = rs + TILE * padded;         // [TILE][padded]
   float* vs = ws + TILE * padded;         // [TILE][cv]
-  float* g0 = vs + TILE * cv;             // [TILE] log input gate | step
-  float* g1 = g0 + TILE;                  // [TILE] log forget gate | decay
+  float* g0 = vs + TILE * cv;             // [TILE] log input gate, then take | step
+  float* g1 = g0 + TILE;                  // [TILE] log forget gate, then keep | decay
+  float* g2 = g1 + TILE;                  // [TILE] running maximum after the row
+  // a thread has the rows g * RPT .. g * RPT + RPT - 1 of column j; the G threads of a column are neighbouring lanes
   const int tid = threadIdx.x, g = tid % G, jl = tid / G;
   const int j = blockIdx.z * cv + jl;
   const bool is_fresh = a.fresh[e] != 0;
   float* head_state = a.state + size_t(a.state_slot[e]) * a.slot_stride + size_t(h) * a.head_stride;
-  float* norm_state = head_state + size_t(rows) * cols + size_t(blockIdx.z) * (rows + 1);
+  // the normaliser and the running maximum are kept NORM_COPIES times: the CTA of slice z reads copy z and renews the
+  // copies z, z + slices, z + 2 slices, ..., so that every copy is current whatever the number of slices of a launch
+  float* norm_state = head_state + size_t(rows) * cols;
 
   if (MODE == MODE_SSD && a.conv_in != nullptr && h == 0 && blockIdx.z == 0) {
     // the inputs of the convolution's last taps - 1 positions: this step's newest rows, and before them what the
@@ -92,11 +96,11 @@ outer_scan_kernel(const ScanArgs a) {
   float S[RPT], nrm[RPT], m = 0.f;
 #pragma unroll
   for (int r = 0; r < RPT; ++r) {
-    const int i = r * G + g;
-    S[r] = (!is_fresh && i < rows && j < cols && jl < cv) ? head_state[size_t(i) * cols + j] : 0.f;
-    nrm[r] = (MODE == MODE_MLSTM && !is_fresh && i < rows) ? norm_state[i] : 0.f;
+    const int i = g * RPT + r;
+    S[r] = (!is_fresh && i < rows && j < cols) ? head_state[size_t(i) * cols + j] : 0.f;
+    nrm[r] = (MODE == MODE_MLSTM && !is_fresh && i < rows) ? norm_state[size_t(blockIdx.z) * (rows + 1) + i] : 0.f;
   }
-  if (MODE == MODE_MLSTM && !is_fresh) m = norm_state[rows];
+  if (MODE == MODE_MLSTM && !is_fresh) m = norm_state[size_t(blockIdx.z) * (rows + 1) + rows];
 
   const T* read = static_cast<const T*>(a.read) + size_t(h / a.heads_per_group) * rows;
   const T* write = static_cast<const T*>(a.write) + size_t(h / a.heads_per_group) * rows;
@@ -106,15 +110,40 @@ outer_scan_kernel(const ScanArgs a) {
   for (int t0 = row0; t0 < row1; t0 += TILE) {
     const int nt = row1 - t0 < TILE ? row1 - t0 : TILE;
     __syncthreads();  // the last rows' vectors have been used
-    for (int idx = tid; idx < nt * padded; idx += blockDim.x) {
-      const int tt = idx / padded, i = idx - tt * padded;
-      const size_t row = size_t(t0 + tt);
-      rs[idx] = i < rows ? to_float(read[row * a.read_stride + i]) * a.read_scale : 0.f;
-      ws[idx] = i < rows ? to_float(write[row * a.write_stride + i]) : 0.f;
+    // (loads in batches of eight before their stores: a loop of load-then-store would wait for every load in turn)
+    for (int base = 0; base < nt * padded; base += 8 * blockDim.x) {
+      float tr[8], tw[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int idx = base + u * blockDim.x + tid;
+        const int tt = idx / padded, i = idx - tt * padded;
+        const bool live = idx < nt * padded && i < rows;
+        const size_t row = size_t(t0 + tt);
+        tr[u] = live ? to_float(read[row * a.read_stride + i]) : 0.f;
+        tw[u] = live ? to_float(write[row * a.write_stride + i]) : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int idx = base + u * blockDim.x + tid;
+        if (idx < nt * padded) {
+          rs[idx] = tr[u] * a.read_scale;
+          ws[idx] = tw[u];
+        }
+      }
     }
-    for (int idx = tid; idx < nt * cv; idx += blockDim.x) {
-      const int tt = idx / cv, c = idx - tt * cv;
-      vs[idx] = blockIdx.z * cv + c < cols ? to_float(value[size_t(t0 + tt) * a.value_stride + c]) : 0.f;
+    for (int base = 0; base < nt * cv; base += 4 * blockDim.x) {
+      float tv[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = base + u * blockDim.x + tid;
+        const int tt = idx / cv, c = idx - tt * cv;
+        tv[u] = (idx < nt * cv && blockIdx.z * cv + c < cols) ? to_float(value[size_t(t0 + tt) * a.value_stride + c]) : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int idx = base + u * blockDim.x + tid;
+        if (idx < nt * cv) vs[idx] = tv[u];
+      }
     }
     if (tid < nt) {
       const float* gr = a.gates + size_t(t0 + tid) * a.gates_stride;
@@ -128,80 +157,130 @@ outer_scan_kernel(const ScanArgs a) {
       }
     }
     __syncthreads();
-    for (int tt = 0; tt < nt; ++tt) {
-      float keep, take;
-      if (MODE == MODE_MLSTM) {
-        const float li = g0[tt], lf = g1[tt];
-        const float m_new = fmaxf(lf + m, li);
-        keep = expf(lf + m - m_new);
-        take = expf(li - m_new);
-        m = m_new;
-      } else {
-        take = g0[tt];
-        keep = g1[tt];
-      }
-      const float v = jl < cv ? vs[tt * cv + jl] : 0.f;
-      const float tv = take * v;
-      const float* wr = ws + tt * padded + g;
-      const float* rr = rs + tt * padded + g;
-      float num = 0.f, nq = 0.f;
-#pragma unroll
-      for (int r = 0; r < RPT; ++r) {
-        const float w = wr[r * G], q = rr[r * G];
-        S[r] = fmaf(keep, S[r], w * tv);
-        num = fmaf(S[r], q, num);
-        if (MODE == MODE_MLSTM) {
-          nrm[r] = fmaf(keep, nrm[r], take * w);
-          nq = fmaf(nrm[r], q, nq);
+    if (MODE == MODE_MLSTM) {
+      // the running maximum is a chain of an addition and a maximum per row: every one of the first nt threads walks
+      // it up to its own row (in the rows' order, so the result does not depend on where a tile begins); the
+      // exponentials, which are what costs, are then one per thread
+      float keep = 0.f, take = 0.f, top = 0.f;
+      if (tid < nt) {
+        float before = m;
+        top = m;
+        for (int tt = 0; tt <= tid; ++tt) {
+          before = top;
+          top = fmaxf(g1[tt] + before, g0[tt]);
         }
+        keep = expf(g1[tid] + before - top);
+        take = expf(g0[tid] - top);
       }
+      __syncthreads();
+      if (tid < nt) {
+        g0[tid] = take;
+        g1[tid] = keep;
+        g2[tid] = top;
+      }
+      __syncthreads();
+      m = g2[nt - 1];
+    }
+    float num[TILE], nq[TILE];
+#pragma unroll
+    for (int tt = 0; tt < TILE; ++tt) {
+      num[tt] = 0.f;
+      nq[tt] = 0.f;
+      if (tt < nt) {
+        const float take = g0[tt], keep = g1[tt];
+        const float tv = take * vs[tt * cv + jl];
+        const float4* wr = reinterpret_cast<const float4*>(ws + tt * padded + g * RPT);
+        const float4* rr = reinterpret_cast<const float4*>(rs + tt * padded + g * RPT);
+        float acc = 0.f, acc_n = 0.f;
+#pragma unroll
+        for (int r4 = 0; r4 < RPT / 4; ++r4) {
+          const float4 w4 = wr[r4], q4 = rr[r4];
+          const float w[4] = {w4.x, w4.y, w4.z, w4.w}, q[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int r = r4 * 4 + u;
+            S[r] = fmaf(keep, S[r], w[u] * tv);
+            acc = fmaf(S[r], q[u], acc);
+            if (MODE == MODE_MLSTM) {
+              nrm[r] = fmaf(keep, nrm[r], take * w[u]);
+              acc_n = fmaf(nrm[r], q[u], acc_n);
+            }
+          }
+        }
+        num[tt] = acc;
+        nq[tt] = acc_n;
+      }
+    }
+    // the sums over a column's rows, for all rows of the tile at once (the shuffles of different rows overlap)
+#pragma unroll
+    for (int tt = 0; tt < TILE; ++tt) {
       for (int o = G >> 1; o > 0; o >>= 1) {
-        num += __shfl_xor_sync(0xffffffffu, num, o);
-        if (MODE == MODE_MLSTM) nq += __shfl_xor_sync(0xffffffffu, nq, o);
+        num[tt] += __shfl_xor_sync(0xffffffffu, num[tt], o);
+        if (MODE == MODE_MLSTM) nq[tt] += __shfl_xor_sync(0xffffffffu, nq[tt], o);
       }
-      if (g == 0 && jl < cv && j < cols) {
-        float y;
-        if (MODE == MODE_MLSTM) y = num / (fmaxf(fabsf(nq), expf(-m)) + 1e-6f);
-        else y = fmaf(skip, v, num);
-        a.out[size_t(t0 + tt) * a.out_stride + size_t(h) * cols + j] = y;
+    }
+    if (g == 0 && j < cols) {
+#pragma unroll
+      for (int tt = 0; tt < TILE; ++tt) {
+        if (tt < nt) {
+          float y;
+          if (MODE == MODE_MLSTM) y = num[tt] / (fmaxf(fabsf(nq[tt]), expf(-g2[tt])) + 1e-6f);
+          else y = fmaf(skip, vs[tt * cv + jl], num[tt]);
+          a.out[size_t(t0 + tt) * a.out_stride + size_t(h) * cols + j] = y;
+        }
       }
     }
   }
 #pragma unroll
   for (int r = 0; r < RPT; ++r) {
-    const int i = r * G + g;
-    if (i < rows && j < cols && jl < cv) head_state[size_t(i) * cols + j] = S[r];
-    if (MODE == MODE_MLSTM && jl == 0 && i < rows) norm_state[i] = nrm[r];
+    const int i = g * RPT + r;
+    if (i < rows && j < cols) head_state[size_t(i) * cols + j] = S[r];
   }
-  if (MODE == MODE_MLSTM && tid == 0) norm_state[rows] = m;
+  if (MODE == MODE_MLSTM && jl == 0) {
+    for (int copy = blockIdx.z; copy < NORM_COPIES; copy += gridDim.z) {
+#pragma unroll
+      for (int r = 0; r < RPT; ++r) {
+        const int i = g * RPT + r;
+        if (i < rows) norm_state[size_t(copy) * (rows + 1) + i] = nrm[r];
+      }
+      if (tid == 0) norm_state[size_t(copy) * (rows + 1) + rows] = m;
+    }
+  }
 }
 
-// How a head's state is spread over threads: rows of a column in a thread's registers (rpt) and over neighbouring
-// lanes (G, a power of two up to 32), columns over the threads of a CTA (cv each) and over CTAs (splits).
+// How a head's state is spread over threads: RPT rows of a column in a thread's registers, a column's rows over G
+// neighbouring lanes (a power of two up to 32), cv columns a CTA and the columns over 1, 2, 4 or 8 CTAs: as few as the
+// 256 threads of a CTA allow, and more while the launch has fewer CTAs than the GPU has SMs.
 struct ScanShape { int rpt, G, threads, cv, splits; };
 
-ScanShape scan_shape(int rows, int cols) {
+ScanShape scan_shape(int rows, int cols, int pairs) {
   ScanShape s;
   s.rpt = 4;
   while (s.rpt < 32 && (rows + s.rpt - 1) / s.rpt > 4) s.rpt *= 2;
   s.G = 1;
   while (s.G * s.rpt < rows) s.G *= 2;
-  s.threads = cols * s.G;
-  s.threads = s.threads > 256 ? 256 : (s.threads + 31) / 32 * 32;
-  s.cv = s.threads / (s.G > 32 ? 32 : s.G);
-  s.splits = (cols + s.cv - 1) / s.cv;
+  const int G = s.G > 32 ? 32 : s.G, per_warp = 32 / G;
+  s.splits = 1;
+  for (;;) {
+    s.cv = ((cols + s.splits - 1) / s.splits + per_warp - 1) / per_warp * per_warp;
+    s.threads = s.cv * G;
+    if (s.splits == NORM_COPIES) break;
+    const bool fits = s.threads <= 256, enough = pairs * s.splits >= 120 || s.threads <= 64;
+    if (fits && enough) break;
+    s.splits *= 2;
+  }
   return s;
 }
 
 template <typename T, int MODE>
 int launch_scan(const ScanArgs& in, int n_entries, int n_heads, cudaStream_t stream) {
   ScanArgs a = in;
-  const ScanShape s = scan_shape(a.rows, a.cols);
+  const ScanShape s = scan_shape(a.rows, a.cols, n_entries * n_heads);
   const int rpt = s.rpt, G = s.G, threads = s.threads, splits = s.splits;
-  if (G > 32) return R2_UNSUPPORTED;
+  if (G > 32 || threads > 256) return R2_UNSUPPORTED;
   a.G = G;
   a.cv = s.cv;
-  const size_t smem = sizeof(float) * (size_t(TILE) * (2 * rpt * G + a.cv) + 2 * TILE);
+  const size_t smem = sizeof(float) * (size_t(TILE) * (2 * rpt * G + a.cv) + 3 * TILE);
   if (smem > 48 * 1024) return R2_UNSUPPORTED;
   dim3 grid(n_entries, n_heads, splits);
   switch (rpt) {
@@ -285,13 +364,46 @@ group_norm_gated_kernel(const float* __restrict__ y, int y_stride, const T* __re
   }
 }
 
+// The same with a CTA per (row, group), for groups of many columns.
+template <typename T>
+__global__ void __launch_bounds__(256)
+group_norm_gated_block_kernel(const float* __restrict__ y, int y_stride, const T* __restrict__ gate, int gate_stride,
+                              const float* __restrict__ weight, T* __restrict__ out, int out_stride, int n_groups,
+                              int group_size, float eps, int gate_first) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[33];
+  const int t = blockIdx.x / n_groups, grp = blockIdx.x % n_groups;
+  const float* yr = y + size_t(t) * y_stride + size_t(grp) * group_size;
+  const T* gr = gate + size_t(t) * gate_stride + size_t(grp) * group_size;
+  const float* wr = weight + size_t(grp) * group_size;
+  T* o = out + size_t(t) * out_stride + size_t(grp) * group_size;
+  float sq = 0.f;
+  for (int d = threadIdx.x; d < group_size; d += blockDim.x) {
+    float v = yr[d];
+    if (gate_first) {
+      const float z = to_float(gr[d]);
+      v *= z / (1.f + expf(-z));
+    }
+    sq = fmaf(v, v, sq);
+  }
+  const float inv = 1.f / sqrtf(block_sum(sq, scratch) / float(group_size) + eps);
+  for (int d = threadIdx.x; d < group_size; d += blockDim.x) {
+    float v = yr[d];
+    const float z = to_float(gr[d]);
+    if (gate_first) v = v * (z / (1.f + expf(-z))) * inv * wr[d];
+    else v = v * inv * wr[d] * (1.f / (1.f + expf(-z)));
+    o[d] = from_float<T>(v);
+  }
+}
+
 }  // namespace
 
-// Floats of one head's state in a request slot: the matrix, and the normaliser vector with the running maximum once
-// per slice of the columns.
+// Floats of one head's state in a request slot: the matrix, and NORM_COPIES times the normaliser vector with the
+// running maximum.
 extern "C" long long r2_mlstm_state_floats(int dim, int vdim) {
   if (dim < 1 || vdim < 1) return 0;
-  return (long long)dim * vdim + (long long)scan_shape(dim, vdim).splits * (dim + 1);
+  return (long long)dim * vdim + (long long)NORM_COPIES * (dim + 1);
 }
 
 // The matrix memory's recurrence over a batch of entries. q, k [T, heads * dim] and v [T, heads * vdim] (slices of a
@@ -365,6 +477,18 @@ extern "C" int r2_group_norm_gated(const float* y, int y_stride, const void* gat
   if (n_rows <= 0) return R2_OK;
   if (n_groups < 1 || group_size < 1) return R2_BAD_SHAPE;
   const long long units = (long long)n_rows * n_groups;
+  if (group_size > 256) {
+    if (dtype == R2_F32) {
+      r2_launch(group_norm_gated_block_kernel<float>, dim3((unsigned)units), dim3(256), size_t(0), stream, y, y_stride, (const float*)gate,
+                gate_stride, weight, (float*)out, out_stride, n_groups, group_size, eps, gate_first);
+    } else if (dtype == R2_BF16) {
+      r2_launch(group_norm_gated_block_kernel<bf16>, dim3((unsigned)units), dim3(256), size_t(0), stream, y, y_stride, (const bf16*)gate,
+                gate_stride, weight, (bf16*)out, out_stride, n_groups, group_size, eps, gate_first);
+    } else {
+      return R2_BAD_DTYPE;
+    }
+    return launch_status();
+  }
   dim3 grid((unsigned)((units + 3) / 4));
   if (dtype == R2_F32) {
     r2_launch(group_norm_gated_kernel<float>, grid, dim3(128), size_t(0), stream, y, y_stride, (const float*)gate, gate_stride,

@@ -143,7 +143,7 @@ def _lib(source: str) -> C.CDLL:
 def build_all(head_dims=()) -> None:
     """Compile every kernel library that does not depend on a model, and the attention kernels
     for the given head sizes (a model compiles its own head size at first use otherwise)."""
-    for source in ("rowwise", "gemm_simt", "gemm_tc", "attention_simt", "attention_prefill_tc", "sampling", "wait_selftest"):
+    for source in ("rowwise", "recurrent", "routing", "gemm_simt", "gemm_tc", "attention_simt", "attention_prefill_tc", "sampling", "wait_selftest"):
         _lib(source)
     kernel_library("sfu_probe")  # (profiling/sfu_probe.py: a measurement, no part of a step)
     for head_dim in head_dims:
@@ -891,7 +891,8 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     `sink` adds one to the softmax's denominator (an extra exp(0) term: the weights sum to less than one); `gate`
     [T, n_heads * v_head_dim] multiplies the output by its sigmoid. `softcap` > 0 caps the scaled scores at
     softcap * tanh(s / softcap); `sinks` (float32 [n_heads]) puts exp(sinks[h]) into head h's denominator; `head_gate`
-    (float32 [T, n_heads]) multiplies head h's output by the sigmoid of its entry: these three are the general kernel's.
+    (float32 [T, n_heads]) multiplies head h's output by the sigmoid of its entry: these three are taken by the general
+    kernel, the mma.sync prefill kernel and the fused decode kernel.
     `decode_only` says that every row is an entry of its own (one new token each) and
     `max_context` bounds the rows' context lengths; `q_start` (int32 [R + 1]) with `n_tiles`, the
     sum over entries of ceil(rows / 64), lets the tensor-core prefill kernel take the batch. They
@@ -919,7 +920,8 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     group = n_heads // max(n_kv_heads, 1)
     # only the general kernel takes a value head size of its own or a head size that is no multiple of 16; kept
     # first keys, a sink and an output gate are taken by both prefill kernels and the fused decode kernel
-    fits = v_head_dim == head_dim and head_dim % 16 == 0 and softcap == 0.0 and sinks is None and head_gate is None
+    fits = v_head_dim == head_dim and head_dim % 16 == 0
+    capped = softcap != 0.0 or sinks is not None or head_gate is not None   # what the tcgen05 kernel does not take
     head_gate_stride = 0
     if sinks is not None:
         _need(sinks, "sinks", torch.float32, 1)
@@ -930,7 +932,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         if head_gate.shape != (n, n_heads):
             raise KernelError(f"attention: head_gate {tuple(head_gate.shape)} is not [T, {n_heads}]")
         head_gate_stride = _rows(head_gate, "head_gate")
-    plain = fits and keep_first == 0 and not sink and gate is None
+    plain = fits and keep_first == 0 and not sink and gate is None and not capped
     if plain and q.dtype == torch.bfloat16 and decode_only and _fast_attention and group in (1, 2, 4, 8):
         lib = _lib_for_head_dim("attention_decode", head_dim)
         n_slices = decode_slices(n, n_kv_heads, max_context, q.device)
@@ -947,7 +949,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         if n_slices > 1:
             count_launches(1)  # the merge kernel
         return out
-    if (fits and q.dtype == torch.bfloat16 and _fast_attention and _prefill_tc and q_start is not None and n_tiles > 0 and head_dim == 64
+    if (fits and not capped and q.dtype == torch.bfloat16 and _fast_attention and _prefill_tc and q_start is not None and n_tiles > 0 and head_dim == 64
             and (plain or _prefill_tc_extras)):
         # tcgen05 form (head size 64, pages of 8, 16, 32 or a multiple of 64 keys): 128-row tiles, one entry to a
         # tile. Also where most tiles are mostly empty (single decoded tokens beside a portion: 64 such rows
@@ -967,11 +969,12 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
             and _rows(q, "q") % 8 == 0 and q.data_ptr() % 16 == 0 and (gate is None or (gate_stride % 2 == 0 and gate.data_ptr() % 4 == 0))):
         _need(q_start, "q_start", torch.int32, 1)
         lib = _lib_for_head_dim("attention_prefill", head_dim)
-        status = lib.r2_attention_prefill(
+        status = lib.r2_attention_prefill_capped(
             _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(k_cache), _p(v_cache), C.c_longlong(page_stride),
             page_size, n_pages, _p(block_tables), block_tables.shape[1], _p(q_start), _p(seq_lens),
             q_start.shape[0] - 1, n_tiles, n_heads, n_kv_heads, C.c_float(scale), window, _p(_workspace(q.device).error),
-            keep_first, int(bool(sink)), _p(gate), gate_stride, int(_exact_weights and not plain), _stream())
+            keep_first, int(bool(sink)), _p(gate), gate_stride, int(_exact_weights and not plain), C.c_float(softcap), _p(sinks),
+            _p(head_gate), head_gate_stride, _stream())
         _check(status, "paged_attention (prefill)")
         _used("attention_prefill")
         return out
@@ -990,11 +993,12 @@ def decode_attention_fused(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Te
                            block_tables: torch.Tensor, row_entry: torch.Tensor, positions: torch.Tensor,
                            seq_lens: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
                            window: int, max_context: int, keep_first: int = 0, sink: bool = False,
-                           gate: torch.Tensor | None = None, exact_weights: bool = False) -> torch.Tensor | None:
+                           gate: torch.Tensor | None = None, exact_weights: bool = False, softcap: float = 0.0,
+                           sinks: torch.Tensor | None = None, head_gate: torch.Tensor | None = None) -> torch.Tensor | None:
     """Decode attention in ONE launch for a batch in which every row is an entry of its own: the
     kernel writes the new keys and values to their cache slots, and the slice that finishes last
     merges all slices of its row. Returns None when it does not take the case (the caller then writes
-    the cache and calls `paged_attention`). `keep_first`, `sink` and `gate` as in `paged_attention`;
+    the cache and calls `paged_attention`). `keep_first`, `sink`, `gate`, `softcap`, `sinks` and `head_gate` as in `paged_attention`;
     `exact_weights` carries the softmax's weights into the second product as two bfloat16 terms."""
     group = n_heads // max(n_kv_heads, 1)
     if not (_fast_attention and _fused_decode and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
@@ -1023,13 +1027,23 @@ def decode_attention_fused(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Te
         if gate.shape != (n, n_heads * head_dim):
             raise KernelError(f"decode attention: gate {tuple(gate.shape)} is not [T, {n_heads} * {head_dim}]")
         gate_stride = _rows(gate, "gate")
+    head_gate_stride = 0
+    if sinks is not None:
+        _need(sinks, "sinks", torch.float32, 1)
+        if sinks.shape[0] != n_heads:
+            raise KernelError(f"decode attention: sinks {tuple(sinks.shape)} is not [{n_heads}]")
+    if head_gate is not None:
+        _need(head_gate, "head_gate", torch.float32, 2)
+        if head_gate.shape != (n, n_heads):
+            raise KernelError(f"decode attention: head_gate {tuple(head_gate.shape)} is not [T, {n_heads}]")
+        head_gate_stride = _rows(head_gate, "head_gate")
     out = torch.empty(n, n_heads * head_dim, dtype=q.dtype, device=q.device)
-    status = lib.r2_attention_decode_fused(
+    status = lib.r2_attention_decode_fused_capped(
         _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(k_cache), _p(v_cache), C.c_longlong(page_stride), page_size,
         n_pages, _p(block_tables), block_tables.shape[1], _p(row_entry), _p(positions), _p(seq_lens), n, n_heads,
         n_kv_heads, C.c_float(scale), window, slices, _p(k_new), _p(v_new), stride, _p(slot_mapping), _p(ws.floats),
         C.c_longlong(ws.floats.numel()), _p(ws.counters), ws.counters.numel(), keep_first, int(bool(sink)), _p(gate),
-        gate_stride, int(bool(exact_weights)), _stream())
+        gate_stride, int(bool(exact_weights)), C.c_float(softcap), _p(sinks), _p(head_gate), head_gate_stride, _stream())
     if status == -4:
         return None
     _check(status, "decode attention (fused)")

@@ -255,6 +255,15 @@ class RotaryWindowAttention:
         q, k, v = proj[:, : self.q_width], proj[:, self.q_width: at], proj[:, at:]
         if self.rot_dims:
             ops.rotate_half(proj, self.n_heads + self.n_kv_heads, self.head_dim, self.rot_dims, self.inv_freq, ctx.positions)
+        if writes_cache and ctx.decode_only and self.v_head_dim == self.head_dim:
+            # one new token per row: the kernel puts the new key and value into the cache itself
+            mixed = ops.decode_attention_fused(
+                q, k, v, ctx.slot_mapping[cache.group], cache.k, cache.v, cache.page_stride, cache.page_size, cache.n_pages,
+                ctx.block_tables[cache.group], ctx.row_entry, ctx.positions, ctx.seq_lens, self.n_heads, self.n_kv_heads,
+                self.head_dim, self.scale, self.window, ctx.max_context, exact_weights=ops.exact_weights(), softcap=self.softcap,
+                sinks=self.sinks, head_gate=gate)
+            if mixed is not None:
+                return mixed
         if writes_cache:
             ops.kv_write(k, v, cache.k, cache.v, ctx.slot_mapping[cache.group], self.n_kv_heads, self.head_dim,
                          cache.page_size, cache.page_stride, cache.n_pages, v_head_dim=self.v_head_dim)
