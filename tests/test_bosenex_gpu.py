@@ -289,14 +289,14 @@ def _attention_case(dtype, heads, kv, dim, vdim, window, softcap, page, lengths,
 ATTENTION_SHAPES = [
     # heads, kv heads, dim, vdim, window, softcap, page
     (4, 2, 32, 32, 44, 20.0, 16), (8, 1, 64, 64, 70, 0.0, 32), (2, 2, 16, 16, 5, 3.0, 8), (3, 1, 24, 40, 9, 0.0, 4),
-    (2, 1, 128, 64, 130, 50.0, 16), (6, 2, 96, 16, 0, 30.0, 8), (5, 5, 48, 48, 1, 0.0, 16),
+    (2, 1, 128, 64, 130, 50.0, 16), (6, 2, 96, 16, 0, 30.0, 8), (5, 5, 48, 48, 1, 0.0, 16), (6, 3, 96, 96, 120, 30.0, 16),
 ]
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("shape", ATTENTION_SHAPES)
 def test_attention_prompts_portions_and_decoded_rows(dtype, shape):
-    for lengths, new_rows in (((150, 37, 201, 64, 9), (150, 2, 77, 1, 9)), ((300, 1, 45, 130), (1, 1, 1, 1))):
+    for lengths, new_rows in (((150, 37, 201, 64, 9), (150, 2, 77, 1, 9)), ((300, 1, 45, 130), (1, 1, 1, 1)), ((700, 333, 64), (700, 1, 3))):
         got, want = _attention_case(dtype, *shape, lengths, new_rows, seed=7)
         for e, (a, b) in enumerate(zip(got, want)):
             close(a, b, dtype, f"{shape} {lengths} entry {e}")
