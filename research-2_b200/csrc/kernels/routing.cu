@@ -10,7 +10,6 @@
 //                     (and of one more expert that every row uses) lie side by side in one row; each expert's
 //                     columns are multiplied by the row's weight for that expert, so that ONE down product over the
 //                     stacked matrices is the weighted sum of the experts' outputs.
-//   r2_expert_decode  for a few rows: each row's chosen experts only, a CTA per (row, choice).
 #include <math.h>
 
 #include "common.cuh"
@@ -76,6 +75,7 @@ route_top_k_kernel(const T* __restrict__ h, int h_stride, const float* __restric
       const int oat = __shfl_xor_sync(0xffffffffu, at, o);
       if (ov > v || (ov == v && oat < at)) { v = ov; at = oat; }
     }
+    if (at >= n_experts) { at = c; v = best0; }   // logits that are not numbers: no index may leave the row
     if (c == 0) best0 = v;
     const float p = expf(v - best0);
     sum += p;

@@ -649,7 +649,9 @@ namespace {
 template <typename T>
 __global__ void __launch_bounds__(256)
 rotate_half_kernel(T* __restrict__ buf, int row_stride, int n_heads, int head_dim, int half, const float* __restrict__ inv_freq,
-                   const int32_t* __restrict__ positions) {
+                   const int32_t* __restrict__ positions, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                   const int32_t* __restrict__ slot_mapping, int k_col, int v_col, int n_kv_heads, int v_head_dim, int page_size,
+                   long long page_stride, int n_pages) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -663,6 +665,22 @@ rotate_half_kernel(T* __restrict__ buf, int row_stride, int n_heads, int head_di
     const float u = to_float(x[i]), v = to_float(x[i + half]);
     x[i] = from_float<T>(u * c - v * s);
     x[i + half] = from_float<T>(v * c + u * s);
+  }
+  if (k_cache == nullptr) return;
+  // the same launch (one CTA a row then) puts the rotated keys and the values into the row's cache slot
+  __syncthreads();
+  const int slot = slot_mapping[t];
+  const int page = slot / page_size, off = slot % page_size;
+  if (slot < 0 || page >= n_pages) return;  // never write outside the pool
+  const T* ks = row + k_col;
+  const T* vs = row + v_col;
+  for (int i = threadIdx.x; i < n_kv_heads * head_dim; i += blockDim.x) {
+    const int h = i / head_dim, d = i % head_dim;
+    k_cache[size_t(page) * page_stride + (size_t(h) * page_size + off) * head_dim + d] = ks[i];
+  }
+  for (int i = threadIdx.x; i < n_kv_heads * v_head_dim; i += blockDim.x) {
+    const int h = i / v_head_dim, d = i % v_head_dim;
+    v_cache[size_t(page) * page_stride + (size_t(h) * page_size + off) * v_head_dim + d] = vs[i];
   }
 }
 
@@ -688,16 +706,23 @@ pair_norm_add_kernel(const float* __restrict__ x, const float* __restrict__ a, c
 }
 }  // namespace
 
+// With k_cache (may be null) the launch also writes the row's keys (columns k_col .., n_kv_heads heads of head_dim, after
+// their rotation) and values (columns v_col .., heads of v_head_dim) to the row's slot of the paged cache.
 extern "C" int r2_rotate_half(void* buf, int row_stride, int n_rows, int n_heads, int head_dim, int rot_dims, const float* inv_freq,
-                              const int32_t* positions, int dtype, cudaStream_t stream) {
-  if (n_rows <= 0 || rot_dims == 0) return R2_OK;
+                              const int32_t* positions, void* k_cache, void* v_cache, const int32_t* slot_mapping, int k_col, int v_col,
+                              int n_kv_heads, int v_head_dim, int page_size, long long page_stride, int n_pages, int dtype,
+                              cudaStream_t stream) {
+  if (n_rows <= 0 || (rot_dims == 0 && k_cache == nullptr)) return R2_OK;
   if (n_heads < 1 || rot_dims < 0 || rot_dims % 2 != 0 || rot_dims > head_dim) return R2_BAD_SHAPE;
+  if (k_cache != nullptr && (v_cache == nullptr || slot_mapping == nullptr || n_kv_heads < 1 || v_head_dim < 1 || page_size < 1)) return R2_BAD_SHAPE;
   const int half = rot_dims / 2;
-  dim3 grid(n_rows, (n_heads * half + 1023) / 1024);
+  dim3 grid(n_rows, k_cache != nullptr ? 1 : (n_heads * half + 1023) / 1024);
   if (dtype == R2_F32) {
-    r2_launch(rotate_half_kernel<float>, grid, dim3(256), size_t(0), stream, (float*)buf, row_stride, n_heads, head_dim, half, inv_freq, positions);
+    r2_launch(rotate_half_kernel<float>, grid, dim3(256), size_t(0), stream, (float*)buf, row_stride, n_heads, head_dim, half, inv_freq, positions,
+              (float*)k_cache, (float*)v_cache, slot_mapping, k_col, v_col, n_kv_heads, v_head_dim, page_size, page_stride, n_pages);
   } else if (dtype == R2_BF16) {
-    r2_launch(rotate_half_kernel<bf16>, grid, dim3(256), size_t(0), stream, (bf16*)buf, row_stride, n_heads, head_dim, half, inv_freq, positions);
+    r2_launch(rotate_half_kernel<bf16>, grid, dim3(256), size_t(0), stream, (bf16*)buf, row_stride, n_heads, head_dim, half, inv_freq, positions,
+              (bf16*)k_cache, (bf16*)v_cache, slot_mapping, k_col, v_col, n_kv_heads, v_head_dim, page_size, page_stride, n_pages);
   } else {
     return R2_BAD_DTYPE;
   }

@@ -545,17 +545,24 @@ def route_top_k(h: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, top
     return dense, chosen, weight
 
 
-def rotate_half(buf: torch.Tensor, n_heads: int, head_dim: int, rot_dims: int, inv_freq: torch.Tensor, positions: torch.Tensor) -> None:
+def rotate_half(buf: torch.Tensor, n_heads: int, head_dim: int, rot_dims: int, inv_freq: torch.Tensor, positions: torch.Tensor,
+                kv: KvScatter | None = None, n_kv_heads: int = 0, k_col: int = 0) -> None:
     """Rotation by position, in place, of the first `n_heads` heads of every row of `buf` (a stacked projection whose
     first columns are the query heads and then the key heads): of each head the first rot_dims dimensions, dimension i
-    paired with i + rot_dims / 2, by the angle position * inv_freq[i] (float32 [rot_dims / 2])."""
+    paired with i + rot_dims / 2, by the angle position * inv_freq[i] (float32 [rot_dims / 2]). With `kv` (see
+    `kv_scatter`: `col` the first value column, `head_dim` the values' head size) the same launch puts the rotated keys
+    (n_kv_heads heads from column `k_col`) and the values into the rows' cache slots."""
     _need(buf, "buf", dim=2)
     _need(inv_freq, "inv_freq", torch.float32, 1)
     _need(positions, "positions", torch.int32, 1)
     if rot_dims % 2 or not 0 <= rot_dims <= head_dim or inv_freq.shape[0] != rot_dims // 2 or buf.shape[1] < n_heads * head_dim:
         raise KernelError(f"rotate_half: {rot_dims} of {head_dim} dimensions, {n_heads} heads in rows of {buf.shape[1]}")
+    if kv is not None and (kv.width != n_kv_heads * kv.head_dim or kv.col + kv.width > buf.shape[1] or k_col + n_kv_heads * head_dim > buf.shape[1]):
+        raise KernelError("rotate_half: the key and value columns do not fit the projection")
+    cache = (C.c_void_p(kv.k_cache), C.c_void_p(kv.v_cache), C.c_void_p(kv.slots), k_col, kv.col, n_kv_heads, kv.head_dim, kv.page_size,
+             C.c_longlong(kv.page_stride), kv.n_pages) if kv is not None else (None, None, None, 0, 0, 0, 0, 0, C.c_longlong(0), 0)
     status = _lib("rowwise").r2_rotate_half(_p(buf), _rows(buf, "buf"), buf.shape[0], n_heads, head_dim, rot_dims, _p(inv_freq),
-                                           _p(positions), dtype_code(buf.dtype), _stream())
+                                           _p(positions), *cache, dtype_code(buf.dtype), _stream())
     _check(status, "rotate_half")
 
 

@@ -253,9 +253,16 @@ class RotaryWindowAttention:
         gate = ops.small_linear(h, self.w_gate, None) if self.w_gate is not None else None
         at = self.q_width + self.k_width
         q, k, v = proj[:, : self.q_width], proj[:, self.q_width: at], proj[:, at:]
-        if self.rot_dims:
+        fused_decode = writes_cache and ctx.decode_only and self.v_head_dim == self.head_dim
+        if writes_cache and not fused_decode:
+            # the rotation's launch also puts the rotated keys and the values into the rows' cache slots
+            scatter = ops.kv_scatter(ctx.slot_mapping[cache.group], cache.k, cache.v, cache.page_stride, cache.page_size,
+                                     cache.n_pages, at, self.v_width, self.v_head_dim)
+            ops.rotate_half(proj, self.n_heads + self.n_kv_heads, self.head_dim, self.rot_dims, self.inv_freq, ctx.positions,
+                            kv=scatter, n_kv_heads=self.n_kv_heads, k_col=self.q_width)
+        elif self.rot_dims:
             ops.rotate_half(proj, self.n_heads + self.n_kv_heads, self.head_dim, self.rot_dims, self.inv_freq, ctx.positions)
-        if writes_cache and ctx.decode_only and self.v_head_dim == self.head_dim:
+        if fused_decode:
             # one new token per row: the kernel puts the new key and value into the cache itself
             mixed = ops.decode_attention_fused(
                 q, k, v, ctx.slot_mapping[cache.group], cache.k, cache.v, cache.page_stride, cache.page_size, cache.n_pages,
@@ -264,7 +271,6 @@ class RotaryWindowAttention:
                 sinks=self.sinks, head_gate=gate)
             if mixed is not None:
                 return mixed
-        if writes_cache:
             ops.kv_write(k, v, cache.k, cache.v, ctx.slot_mapping[cache.group], self.n_kv_heads, self.head_dim,
                          cache.page_size, cache.page_stride, cache.n_pages, v_head_dim=self.v_head_dim)
         return ops.paged_attention(

@@ -112,10 +112,8 @@ class RoutedExperts:
     All experts' input projections are stacked into one matrix ([gates of every expert; shared gate; ups of every expert;
     shared up]) and their down matrices side by side into another, so that a layer is two dense products: the
     activation between them multiplies an expert's columns by the row's weight for that expert (zero where it was not
-    chosen), and the second product's sum over all columns is the weighted sum over experts. For a few rows
-    (`sparse_rows` or fewer) only the chosen experts' weights are read: a kernel walks each row's choices."""
-
-    sparse_rows = 0   # (the dense form serves every batch until a kernel for the chosen experts alone is there)
+    chosen), and the second product's sum over all columns is the weighted sum over experts. Every step reads all
+    experts' weights; a form that reads only the chosen ones for a few rows is not built."""
 
     def __init__(self, params: dict, weights: dict, rt: Runtime):
         self.n_experts, self.top = int(params["n_experts"]), int(params["top"])
