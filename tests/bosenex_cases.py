@@ -96,6 +96,48 @@ CASES = {
 }
 
 
+def _divisors(n: int) -> list[int]:
+    return [d for d in range(1, n + 1) if n % d == 0]
+
+
+def random_case(seed: int) -> dict:
+    """A configuration drawn from a seed: one to five layers of either kind in any order, sizes that are and are not
+    multiples of 16, every optional mechanism there or not."""
+    import random
+
+    rng = random.Random(seed)
+    layers = []
+    for _ in range(rng.randint(1, 5)):
+        if rng.random() < 0.5:
+            mixer = memory(rng.randint(1, 6), rng.choice([4, 8, 12, 16, 24, 32, 48, 64, 96]), rng.choice([4, 8, 16, 20, 32, 48, 64, 96, 128]),
+                           cap=rng.choice([None, 5.0, 15.0, 30.0]))
+        else:
+            heads = rng.randint(1, 8)
+            dim = rng.choice([8, 16, 24, 32, 48, 64, 80, 96, 128])
+            rot = None
+            if rng.random() < 0.8:
+                rot = (rng.choice(list(range(2, dim + 1, 2))) if rng.random() < 0.4 else dim, rng.choice([100.0, 10000.0, 500000.0]))
+            left = attention(heads, rng.choice(_divisors(heads)), dim, rng.choice([dim, dim, 8, 16, 32, 40, 64]), rng.choice([dim ** -0.5, 0.1, 0.3]),
+                             window=rng.choice([None, 1, 3, 16, 17, 64, 100, 136, 1000]), rot=rot, softcap=rng.choice([None, 10.0, 30.0, 50.0]))
+            s_heads, s_vdim = rng.randint(1, 6), rng.choice([4, 8, 16, 24, 32, 48, 64])
+            right = space(s_heads, s_vdim, rng.choice([4, 8, 16, 32, 64, 128]), rng.choice(_divisors(s_heads)), rng.randint(1, 4),
+                          rng.choice(_divisors(s_heads * s_vdim)[:6]))
+            mixer = {"left": left, "right": right}
+        r = rng.random()
+        if r < 0.15:
+            mlp = None
+        elif r < 0.45:
+            mlp = dense(rng.choice([16, 40, 64, 96, 200]))
+        else:
+            experts = rng.randint(2, 12)
+            mlp = moe(experts, rng.randint(1, min(experts, 4)), rng.choice([8, 16, 24, 32, 64]), rng.choice([0.5, 1.0, 7.0]),
+                      shared=(rng.choice([8, 16, 48]), rng.choice([0.5, 1.5])) if rng.random() < 0.6 else None)
+        layers.append(layer(mixer, mlp))
+    config = model(rng.choice([50, 97, 256, 1000]), rng.choice([24, 40, 64, 72, 100, 128, 192, 320]), layers, eps=rng.choice([1e-6, 1e-5]),
+                   embedding_scale=rng.choice([None, 1.0, 4.0, 16.0]), logit_scale=rng.choice([None, 0.25, 1.0, 2.0]))
+    return {"config": config, "seed": seed, "std": 0.06, "page_size": rng.choice([4, 8, 16, 32]), "length": rng.choice([40, 150, 300])}
+
+
 def make_model_dir(folder: Path, case: dict, store_dtype: str = "bfloat16") -> Path:
     from research_2_b200 import models  # noqa: F401  (registers the architectures)
     from research_2_b200.config.registry import architecture_of

@@ -14,7 +14,7 @@ import pytest
 import torch
 
 from tests import traces
-from tests.bosenex_cases import CASES, assert_close_to_plain, make_model_dir, plain_logits, random_tokens
+from tests.bosenex_cases import CASES, assert_close_to_plain, make_model_dir, plain_logits, random_case, random_tokens
 from tests.plain import bosenex_plain as plain
 
 pytestmark = pytest.mark.gpu
@@ -400,6 +400,21 @@ def test_cuttings(folders, name, dtype, mode):
         assert traces.max_live(tb) == 4 and len(requests) > 4, "state slots are used again"
         if replay.model.cache_members:
             assert reused >= 4, f"only {reused} pages passed from one request to another"
+
+
+@pytest.mark.parametrize("seed", range(100, 108))
+def test_configurations_drawn_at_random(seed, tmp_path):
+    """Layers in any order and sizes of any kind: float32 within its floor in three cuttings, bfloat16 within its own
+    (positions at which the design is discontinuous excused)."""
+    case = random_case(seed)
+    folder = make_model_dir(tmp_path / "model", case)
+    ids = random_tokens(seed, case["length"], case["config"]["vocab"])
+    requests = {"x": ids, "y": ids[: max(3, len(ids) // 3)], "z": ids[5:]}
+    for dtype, modes in (("float32", ("whole", "portions", "mixed")), ("bfloat16", ("mixed",))):
+        for mode in modes:
+            tb = cut(requests, mode) if mode != "mixed" else traces.mixed(requests, max_live=2)
+            outputs, _, _ = run_trace(folder, tb, dtype, case["page_size"])
+            compare(folder, requests, tb, outputs, dtype, f"seed {seed} {dtype} {mode}")
 
 
 def test_float32_logits_do_not_depend_on_the_cutting_at_all(folders):
