@@ -22,7 +22,9 @@
 
 namespace {
 
-constexpr int TILE = 16;       // rows whose vectors are staged at a time
+// Rows whose vectors are staged at a time: 32 (16 where a thread has 32 rows of a column in registers); 4 for launches in
+// which every entry is a single decoded row (less shared memory: more CTAs to an SM).
+constexpr int MAX_TILE = 32, SMALL_TILE = 4;
 constexpr int NORM_COPIES = 8;  // copies of a matrix memory's normaliser and maximum: one per slice of the columns at most
 
 constexpr int MODE_MLSTM = 0, MODE_SSD = 1;
@@ -47,11 +49,12 @@ struct ScanArgs {
   const int32_t* q_start; const int32_t* state_slot; const int32_t* fresh;
   float* out; int out_stride;            // [T, heads * cols] float
   int heads_per_group, rows, cols, G, cv;
+  int single_rows;                       // a hint: no entry has more than one row (a decode step)
   // state space: the convolution's last inputs, kept by the CTA of (entry, head 0, slice 0)
   const void* conv_in; int conv_in_stride; int conv_channels, conv_taps; long long conv_state_off;
 };
 
-template <typename T, int RPT, int MODE>
+template <typename T, int RPT, int MODE, int TILE>
 __global__ void __launch_bounds__(256)
 outer_scan_kernel(const ScanArgs a) {
   pdl_launch_dependents();
@@ -163,11 +166,20 @@ outer_scan_kernel(const ScanArgs a) {
       // exponentials, which are what costs, are then one per thread
       float keep = 0.f, take = 0.f, top = 0.f;
       if (tid < nt) {
+        float li[TILE], lf[TILE];   // (all loads first: the chain is then an addition and a maximum a row)
+#pragma unroll
+        for (int tt = 0; tt < TILE; ++tt) {
+          li[tt] = g0[tt];
+          lf[tt] = g1[tt];
+        }
         float before = m;
         top = m;
-        for (int tt = 0; tt <= tid; ++tt) {
-          before = top;
-          top = fmaxf(g1[tt] + before, g0[tt]);
+#pragma unroll
+        for (int tt = 0; tt < TILE; ++tt) {
+          if (tt <= tid) {
+            before = top;
+            top = fmaxf(lf[tt] + before, li[tt]);
+          }
         }
         keep = expf(g1[tid] + before - top);
         take = expf(g0[tid] - top);
@@ -184,9 +196,10 @@ outer_scan_kernel(const ScanArgs a) {
     float num[TILE], nq[TILE];
 #pragma unroll
     for (int tt = 0; tt < TILE; ++tt) {
+      if (tt >= nt) break;   // (a branch that every thread of the CTA takes alike: rows that are not there cost nothing)
       num[tt] = 0.f;
       nq[tt] = 0.f;
-      if (tt < nt) {
+      {
         const float take = g0[tt], keep = g1[tt];
         const float tv = take * vs[tt * cv + jl];
         const float4* wr = reinterpret_cast<const float4*>(ws + tt * padded + g * RPT);
@@ -214,15 +227,19 @@ outer_scan_kernel(const ScanArgs a) {
     // the sums over a column's rows, for all rows of the tile at once (the shuffles of different rows overlap)
 #pragma unroll
     for (int tt = 0; tt < TILE; ++tt) {
-      for (int o = G >> 1; o > 0; o >>= 1) {
-        num[tt] += __shfl_xor_sync(0xffffffffu, num[tt], o);
-        if (MODE == MODE_MLSTM) nq[tt] += __shfl_xor_sync(0xffffffffu, nq[tt], o);
+      if (tt >= nt) break;
+      {
+        for (int o = G >> 1; o > 0; o >>= 1) {
+          num[tt] += __shfl_xor_sync(0xffffffffu, num[tt], o);
+          if (MODE == MODE_MLSTM) nq[tt] += __shfl_xor_sync(0xffffffffu, nq[tt], o);
+        }
       }
     }
     if (g == 0 && j < cols) {
 #pragma unroll
       for (int tt = 0; tt < TILE; ++tt) {
-        if (tt < nt) {
+        if (tt >= nt) break;
+        {
           float y;
           if (MODE == MODE_MLSTM) y = num[tt] / (fmaxf(fabsf(nq[tt]), expf(-g2[tt])) + 1e-6f);
           else y = fmaf(skip, vs[tt * cv + jl], num[tt]);
@@ -280,15 +297,19 @@ int launch_scan(const ScanArgs& in, int n_entries, int n_heads, cudaStream_t str
   if (G > 32 || threads > 256) return R2_UNSUPPORTED;
   a.G = G;
   a.cv = s.cv;
-  const size_t smem = sizeof(float) * (size_t(TILE) * (2 * rpt * G + a.cv) + 3 * TILE);
+  const bool single_rows = a.single_rows != 0;
+  const int tile = single_rows ? SMALL_TILE : (rpt <= 16 ? MAX_TILE : 16);
+  const size_t smem = sizeof(float) * (size_t(tile) * (2 * rpt * G + a.cv) + 3 * tile);
   if (smem > 48 * 1024) return R2_UNSUPPORTED;
   dim3 grid(n_entries, n_heads, splits);
+#define R2_SCAN(RPT_, TILE_) r2_launch(outer_scan_kernel<T, RPT_, MODE, TILE_>, grid, dim3(threads), smem, stream, a)
   switch (rpt) {
-    case 4: r2_launch(outer_scan_kernel<T, 4, MODE>, grid, dim3(threads), smem, stream, a); break;
-    case 8: r2_launch(outer_scan_kernel<T, 8, MODE>, grid, dim3(threads), smem, stream, a); break;
-    case 16: r2_launch(outer_scan_kernel<T, 16, MODE>, grid, dim3(threads), smem, stream, a); break;
-    default: r2_launch(outer_scan_kernel<T, 32, MODE>, grid, dim3(threads), smem, stream, a); break;
+    case 4: if (single_rows) R2_SCAN(4, SMALL_TILE); else R2_SCAN(4, MAX_TILE); break;
+    case 8: if (single_rows) R2_SCAN(8, SMALL_TILE); else R2_SCAN(8, MAX_TILE); break;
+    case 16: if (single_rows) R2_SCAN(16, SMALL_TILE); else R2_SCAN(16, MAX_TILE); break;
+    default: if (single_rows) R2_SCAN(32, SMALL_TILE); else R2_SCAN(32, 16); break;
   }
+#undef R2_SCAN
   return launch_status();
 }
 
@@ -412,8 +433,8 @@ extern "C" long long r2_mlstm_state_floats(int dim, int vdim) {
 extern "C" int r2_mlstm_scan(const void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride,
                              const float* gates, int gates_stride, float cap, float q_scale, float* state,
                              long long slot_stride, const int32_t* q_start, const int32_t* state_slot, const int32_t* fresh,
-                             int n_entries, float* out, int out_stride, int n_heads, int dim, int vdim, int dtype,
-                             cudaStream_t stream) {
+                             int n_entries, float* out, int out_stride, int n_heads, int dim, int vdim, int single_rows,
+                             int dtype, cudaStream_t stream) {
   if (n_entries <= 0) return R2_OK;
   if (n_heads < 1 || dim < 1 || vdim < 1) return R2_BAD_SHAPE;
   ScanArgs a = {};
@@ -421,7 +442,7 @@ extern "C" int r2_mlstm_scan(const void* q, int q_stride, const void* k, int k_s
   a.gates = gates; a.gates_stride = gates_stride; a.cap = cap; a.read_scale = q_scale;
   a.state = state; a.slot_stride = slot_stride; a.head_stride = int(r2_mlstm_state_floats(dim, vdim));
   a.q_start = q_start; a.state_slot = state_slot; a.fresh = fresh; a.out = out; a.out_stride = out_stride;
-  a.heads_per_group = 1; a.rows = dim; a.cols = vdim;
+  a.heads_per_group = 1; a.rows = dim; a.cols = vdim; a.single_rows = single_rows;
   if (dtype == R2_F32) return launch_scan<float, MODE_MLSTM>(a, n_entries, n_heads, stream);
   if (dtype == R2_BF16) return launch_scan<bf16, MODE_MLSTM>(a, n_entries, n_heads, stream);
   return R2_BAD_DTYPE;
@@ -436,7 +457,8 @@ extern "C" int r2_ssd_scan(const void* x, int x_stride, const void* b, int b_str
                            const float* skip, float* state, long long slot_stride, const int32_t* q_start,
                            const int32_t* state_slot, const int32_t* fresh, int n_entries, float* out, int out_stride,
                            int n_heads, int n_groups, int n_state, int vdim, const void* conv_in, int conv_in_stride,
-                           int conv_channels, int conv_taps, long long conv_state_off, int dtype, cudaStream_t stream) {
+                           int conv_channels, int conv_taps, long long conv_state_off, int single_rows, int dtype,
+                           cudaStream_t stream) {
   if (n_entries <= 0) return R2_OK;
   if (n_heads < 1 || n_groups < 1 || n_heads % n_groups != 0 || n_state < 1 || vdim < 1) return R2_BAD_SHAPE;
   ScanArgs a = {};
@@ -444,7 +466,7 @@ extern "C" int r2_ssd_scan(const void* x, int x_stride, const void* b, int b_str
   a.gates = steps; a.gates_stride = steps_stride; a.step_bias = step_bias; a.log_rate = log_rate; a.skip = skip;
   a.read_scale = 1.f; a.state = state; a.slot_stride = slot_stride; a.head_stride = n_state * vdim;
   a.q_start = q_start; a.state_slot = state_slot; a.fresh = fresh; a.out = out; a.out_stride = out_stride;
-  a.heads_per_group = n_heads / n_groups; a.rows = n_state; a.cols = vdim;
+  a.heads_per_group = n_heads / n_groups; a.rows = n_state; a.cols = vdim; a.single_rows = single_rows;
   a.conv_in = conv_taps > 1 ? conv_in : nullptr; a.conv_in_stride = conv_in_stride; a.conv_channels = conv_channels;
   a.conv_taps = conv_taps; a.conv_state_off = conv_state_off;
   if (dtype == R2_F32) return launch_scan<float, MODE_SSD>(a, n_entries, n_heads, stream);

@@ -621,7 +621,7 @@ def mlstm_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gates: torch.T
     status = _lib("recurrent").r2_mlstm_scan(
         _p(q), _rows(q, "q"), _p(k), _rows(k, "k"), _p(v), _rows(v, "v"), _p(gates), _rows(gates, "gates"), C.c_float(cap),
         C.c_float(q_scale), _p(state), C.c_longlong(state.shape[1]), _p(q_start), _p(state_slot), _p(fresh), n, _p(out),
-        _rows(out, "out"), n_heads, dim, vdim, dtype_code(q.dtype), _stream())
+        _rows(out, "out"), n_heads, dim, vdim, int(q.shape[0] <= n), dtype_code(q.dtype), _stream())
     _check(status, "mlstm_scan")
     return out
 
@@ -683,7 +683,7 @@ def ssd_scan(x: torch.Tensor, b: torch.Tensor, c: torch.Tensor, steps: torch.Ten
         _p(x), _rows(x, "x"), _p(b), _rows(b, "b"), _p(c), _rows(c, "c"), _p(steps), _rows(steps, "steps"), _p(step_bias),
         _p(log_rate), _p(skip), _p(state), C.c_longlong(state.shape[1]), _p(q_start), _p(state_slot), _p(fresh), n, _p(out),
         _rows(out, "out"), n_heads, n_groups, n_state, vdim, _p(conv_in), 0 if conv_in is None else _rows(conv_in, "conv_in"),
-        channels, conv_taps, C.c_longlong(conv_state_off), dtype_code(x.dtype), _stream())
+        channels, conv_taps, C.c_longlong(conv_state_off), int(x.shape[0] <= n), dtype_code(x.dtype), _stream())
     _check(status, "ssd_scan")
     return out
 
